@@ -1,0 +1,45 @@
+"""Shared plumbing of the collective entry points: algorithm naming, async launch."""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+
+from . import schedule as sch
+from .comm import Group
+from .request import Request
+
+
+def algo_from_flags(algorithm: Optional[str], recursive_flag: bool) -> str:
+    """The reference selects with booleans (``use_rd`` / ``use_rh``: recursive, else ring);
+    ``algorithm`` is this library's wider choice and wins when given."""
+    if algorithm is not None:
+        if algorithm != sch.AUTO and algorithm not in sch.ALGO_IDS:
+            raise ValueError(f"unknown algorithm {algorithm!r}")
+        return algorithm
+    return sch.RECURSIVE if recursive_flag else sch.RING
+
+
+def run_native(group: Group, async_op: bool, launch: Callable[[], None]) -> Optional[Request]:
+    """Enqueue ``launch()`` on the current stream, or, for ``async_op``, on the
+    communicator's side stream after everything the current stream has queued so far."""
+    comm = group.comm
+    if not async_op:
+        launch()
+        return None
+    cur = torch.cuda.current_stream(comm.device)
+    side = comm.side_stream()
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        launch()
+        ev = torch.cuda.Event()
+        ev.record(side)
+    return Request(ev, comm)
+
+
+class _Done:
+    _pccl_completed = True
+
+
+def completed_request() -> Request:
+    return Request(_Done())

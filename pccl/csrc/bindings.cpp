@@ -1,0 +1,507 @@
+// Python bindings of the native layer (module pccl._C).
+//
+// Role of pccl/src/pccl.cpp in the reference (reduce_scatter_mpi / all_gather_mpi with
+// their argument checks, :11-148) and of the unbuilt pccl/src/yacl.cpp (all_reduce_mpi,
+// :146-184).  Differences: sizes are 64-bit, bf16/fp16/fp32 are accepted for the
+// reductions (the reference takes fp32 only, pccl.cpp:42-45), the algorithm is an enum
+// that includes ring all-gather, and errors surface as Python exceptions.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include <optional>
+
+#include "comm.h"
+#include "schedule.h"
+#include "segments.h"
+
+namespace py = pybind11;
+using namespace pccl;
+
+namespace {
+
+int to_dtype(at::ScalarType t) {
+  switch (t) {
+    case at::kBFloat16: return kBF16;
+    case at::kHalf: return kF16;
+    case at::kFloat: return kF32;
+    default: throw Error("unsupported dtype for a reduction: expected bfloat16, float16 or float32");
+  }
+}
+
+py::tuple step_tuple(const Step& s) { return py::make_tuple(s.dst, s.src, s.send_first, s.recv_first, s.nblocks); }
+
+cudaStream_t current_stream(int device) { return at::cuda::getCurrentCUDAStream(device).stream(); }
+
+void check_tensor(const at::Tensor& t, const char* name, int device) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.get_device() == device, name, " lives on cuda:", t.get_device(), ", the communicator on cuda:", device);
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+struct LocalList {
+  int n;          // number of local ranks driven by this call
+  int first;      // group index of local slot 0
+};
+
+LocalList local_list(Comm& c, int gid, size_t given, const char* what) {
+  const GroupState& gs = c.group(gid);
+  TORCH_CHECK(gs.my_index >= 0, "this rank is not a member of the group");
+  LocalList l;
+  l.n = c.nlocal() > 1 ? (int)gs.ranks.size() : 1;
+  l.first = c.nlocal() > 1 ? 0 : gs.my_index;
+  TORCH_CHECK((int)given == l.n, what, ": expected ", l.n, " tensor(s), one per local rank, got ", given);
+  return l;
+}
+
+// Offset of tensor i inside the heap of the rank that owns local slot i; all slots must
+// agree (the buffer is symmetric) or none may be in the heap.
+int64_t symmetric_offset(Comm& c, int gid, const LocalList& l, const std::vector<at::Tensor>& ts) {
+  const GroupState& gs = c.group(gid);
+  int64_t off = -2;
+  for (int i = 0; i < l.n; ++i) {
+    const int owner = gs.ranks[l.first + i];
+    const int64_t o = c.offset_of((uint64_t)ts[i].data_ptr(), (uint64_t)ts[i].nbytes(), owner);
+    if (off == -2) off = o;
+    TORCH_CHECK(o == off, "tensors of the emulated ranks are not at the same heap offset");
+  }
+  return off;
+}
+
+// ------------------------------------------------------------------ flat all-gather
+void all_gather(Comm& c, int gid, std::vector<at::Tensor> outs, std::vector<at::Tensor> ins, int algo, int nlanes) {
+  const LocalList l = local_list(c, gid, outs.size(), "all_gather outputs");
+  TORCH_CHECK(ins.size() == outs.size(), "all_gather: need one input per output");
+  const int P = c.group_size(gid);
+  const int dev = c.device();
+  c10::cuda::CUDAGuard guard(dev);
+  for (int i = 0; i < l.n; ++i) {
+    check_tensor(outs[i], "output_tensor", dev);
+    check_tensor(ins[i], "input_tensor", dev);
+    TORCH_CHECK(outs[i].scalar_type() == ins[i].scalar_type(), "input and output dtypes differ");
+    TORCH_CHECK(outs[i].numel() == ins[i].numel() * P, "output_tensor must hold world_size * input elements (", P, " * ",
+                ins[i].numel(), "), got ", outs[i].numel());
+    TORCH_CHECK(ins[i].nbytes() == ins[0].nbytes(), "all ranks must contribute the same number of bytes");
+  }
+  const uint64_t n = (uint64_t)ins[0].nbytes();
+  if (n == 0) return;
+  cudaStream_t stream = current_stream(dev);
+  const int64_t out_off = symmetric_offset(c, gid, l, outs);
+  const int64_t in_off = symmetric_offset(c, gid, l, ins);
+
+  AllGatherArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.algo = algo;
+  a.nsub = 1;
+  a.out_src_stride = n;
+  a.in_sub_stride = n;
+  if (algo == kMultimem) TORCH_CHECK(n % 16 == 0, "multimem all-gather needs a multiple of 16 bytes per rank");
+
+  if (algo == kPull) {
+    // Results go straight to the outputs; only a private input needs staging.
+    uint64_t cap = n;
+    if (in_off < 0) {
+      cap = c.staging_bytes() / 16 * 16;
+      TORCH_CHECK(cap > 0, "no staging area configured for non-symmetric tensors");
+    }
+    for (uint64_t e0 = 0; e0 < n; e0 += cap) {
+      const uint64_t len = std::min(cap, n - e0);
+      a.sub_bytes = len;
+      for (int i = 0; i < l.n; ++i) {
+        a.in[i] = in_off < 0 ? (const char*)ins[i].data_ptr() + e0 : nullptr;
+        a.out[i] = (char*)outs[i].data_ptr() + e0;
+      }
+      a.in_off = in_off < 0 ? c.staging_off() : (uint64_t)in_off + e0;
+      a.recv_off = 0;
+      c.all_gather(gid, a, nlanes, stream);
+    }
+    return;
+  }
+
+  if (out_off >= 0) {
+    // Zero-copy: peers write into the symmetric output.
+    if (algo == kMultimem) TORCH_CHECK(out_off % 16 == 0, "multimem needs a 16-byte aligned symmetric output");
+    a.recv_off = (uint64_t)out_off;
+    a.src_stride = n;
+    a.sub_bytes = n;
+    for (int i = 0; i < l.n; ++i) {
+      const bool aliased = (const char*)ins[i].data_ptr() == (const char*)outs[i].data_ptr() + (uint64_t)(l.first + i) * n;
+      a.in[i] = aliased ? nullptr : (const char*)ins[i].data_ptr();
+      a.out[i] = nullptr;
+    }
+    c.all_gather(gid, a, nlanes, stream);
+    return;
+  }
+
+  // Private output: land in the staging area, then copy out inside the same kernel.
+  const uint64_t cap = c.staging_bytes() / P / 16 * 16;
+  TORCH_CHECK(cap > 0, "no staging area configured for non-symmetric tensors");
+  for (uint64_t e0 = 0; e0 < n; e0 += cap) {
+    const uint64_t len = std::min(cap, n - e0);
+    a.recv_off = c.staging_off();
+    a.src_stride = cap;
+    a.sub_bytes = len;
+    for (int i = 0; i < l.n; ++i) {
+      a.in[i] = (const char*)ins[i].data_ptr() + e0;
+      a.out[i] = (char*)outs[i].data_ptr() + e0;
+    }
+    c.all_gather(gid, a, nlanes, stream);
+  }
+}
+
+// Layout-general all-gather used by the 2-D hierarchy: every quantity is given in bytes.
+void all_gather_raw(Comm& c, int gid, int algo, int nlanes, std::vector<uint64_t> in_ptrs, std::vector<uint64_t> out_ptrs,
+                    uint64_t recv_off, uint64_t out_src_stride, uint64_t out_sub_stride, uint64_t src_stride,
+                    uint64_t sub_stride, uint64_t sub_bytes, uint64_t in_sub_stride, int nsub, uint64_t in_off) {
+  const LocalList l = local_list(c, gid, in_ptrs.size(), "all_gather_raw inputs");
+  TORCH_CHECK(out_ptrs.size() == in_ptrs.size(), "all_gather_raw: need one output slot per input");
+  c10::cuda::CUDAGuard guard(c.device());
+  AllGatherArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.algo = algo;
+  for (int i = 0; i < l.n; ++i) {
+    a.in[i] = (const char*)in_ptrs[i];
+    a.out[i] = (char*)out_ptrs[i];
+  }
+  a.recv_off = recv_off;
+  a.out_src_stride = out_src_stride;
+  a.out_sub_stride = out_sub_stride;
+  a.src_stride = src_stride;
+  a.sub_stride = sub_stride;
+  a.sub_bytes = sub_bytes;
+  a.in_sub_stride = in_sub_stride;
+  a.nsub = nsub;
+  a.in_off = in_off;
+  if (sub_bytes == 0) return;
+  c.all_gather(gid, a, nlanes, current_stream(c.device()));
+}
+
+// ------------------------------------------------------------------ flat reduce-scatter
+void reduce_scatter(Comm& c, int gid, std::vector<at::Tensor> outs, std::vector<at::Tensor> ins, int algo, int nlanes,
+                    double scale, std::optional<at::ScalarType> wire) {
+  const LocalList l = local_list(c, gid, outs.size(), "reduce_scatter outputs");
+  TORCH_CHECK(ins.size() == outs.size(), "reduce_scatter: need one input per output");
+  const int P = c.group_size(gid);
+  const int dev = c.device();
+  c10::cuda::CUDAGuard guard(dev);
+  for (int i = 0; i < l.n; ++i) {
+    check_tensor(outs[i], "output_tensor", dev);
+    check_tensor(ins[i], "input_tensor", dev);
+    TORCH_CHECK(ins[i].numel() % P == 0, "input_tensor numel (", ins[i].numel(), ") must be divisible by world size ", P);
+    TORCH_CHECK(outs[i].numel() == ins[i].numel() / P, "output_tensor must hold input numel / world_size elements");
+    TORCH_CHECK(ins[i].numel() == ins[0].numel() && ins[i].scalar_type() == ins[0].scalar_type() &&
+                    outs[i].scalar_type() == outs[0].scalar_type(),
+                "all ranks must pass tensors of the same size and dtype");
+  }
+  const int tin = to_dtype(ins[0].scalar_type());
+  const int tout = to_dtype(outs[0].scalar_type());
+  const int tw = wire.has_value() ? to_dtype(*wire) : tin;
+  TORCH_CHECK(tw == tin || tw == kF32, "partial sums travel in the input dtype or in float32");
+  TORCH_CHECK(tout == tin || tout == kF32 || (tin == kF32 && tout == kBF16),
+              "output dtype must be the input dtype or float32");
+  const uint64_t n = (uint64_t)outs[0].numel();
+  if (n == 0) return;
+  cudaStream_t stream = current_stream(dev);
+  const int64_t in_off = symmetric_offset(c, gid, l, ins);
+  const uint64_t si = dtype_size(tin), sw = dtype_size(tw), so = dtype_size(tout);
+
+  ReduceScatterArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.algo = algo;
+  a.in_dtype = tin;
+  a.wire_dtype = tw;
+  a.out_dtype = tout;
+  a.nsub = 1;
+  a.scale = (float)scale;
+  a.dst_stride = n * si;
+  a.out_sub_stride = n * so;
+
+  if (algo == kPull || algo == kMultimem) {
+    TORCH_CHECK(in_off >= 0, "the pull and multimem reduce-scatter read the peers' inputs: allocate input_tensor "
+                             "with pccl.empty_symmetric or pick another algorithm");
+    if (algo == kMultimem) {
+      TORCH_CHECK(in_off % 16 == 0 && (n * si) % 16 == 0, "multimem reduce-scatter needs 16-byte aligned blocks");
+      TORCH_CHECK(tw == tin, "multimem reduce-scatter has no wire dtype");
+    }
+    a.in_off = (uint64_t)in_off;
+    a.sub_elems = n;
+    for (int i = 0; i < l.n; ++i) {
+      a.in[i] = nullptr;
+      a.out[i] = (char*)outs[i].data_ptr();
+    }
+    c.reduce_scatter(gid, a, nlanes, stream);
+    return;
+  }
+
+  // Push variants: partial sums land in the staging area of the receiver.
+  uint64_t cap = n;
+  if (P > 1) {
+    cap = c.staging_bytes() / (uint64_t)(P - 1) / sw / 8 * 8;
+    TORCH_CHECK(cap > 0, "staging area too small for a reduce-scatter");
+  }
+  for (uint64_t e0 = 0; e0 < n; e0 += cap) {
+    const uint64_t len = std::min(cap, n - e0);
+    a.stage_off = c.staging_off();
+    a.sub_elems = len;
+    for (int i = 0; i < l.n; ++i) {
+      a.in[i] = (const char*)ins[i].data_ptr() + e0 * si;
+      a.out[i] = (char*)outs[i].data_ptr() + e0 * so;
+    }
+    c.reduce_scatter(gid, a, nlanes, stream);
+  }
+}
+
+void reduce_scatter_raw(Comm& c, int gid, int algo, int nlanes, int in_dtype, int wire_dtype, int out_dtype,
+                        std::vector<uint64_t> in_ptrs, std::vector<uint64_t> out_ptrs, uint64_t in_off, uint64_t stage_off,
+                        uint64_t dst_stride, uint64_t sub_stride, uint64_t sub_elems, uint64_t out_sub_stride, int nsub,
+                        double scale) {
+  const LocalList l = local_list(c, gid, in_ptrs.size(), "reduce_scatter_raw inputs");
+  TORCH_CHECK(out_ptrs.size() == in_ptrs.size(), "reduce_scatter_raw: need one output per input");
+  c10::cuda::CUDAGuard guard(c.device());
+  ReduceScatterArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.algo = algo;
+  a.in_dtype = in_dtype;
+  a.wire_dtype = wire_dtype;
+  a.out_dtype = out_dtype;
+  for (int i = 0; i < l.n; ++i) {
+    a.in[i] = (const char*)in_ptrs[i];
+    a.out[i] = (char*)out_ptrs[i];
+  }
+  a.in_off = in_off;
+  a.stage_off = stage_off;
+  a.dst_stride = dst_stride;
+  a.sub_stride = sub_stride;
+  a.sub_elems = sub_elems;
+  a.out_sub_stride = out_sub_stride;
+  a.nsub = nsub;
+  a.scale = (float)scale;
+  if (sub_elems == 0) return;
+  c.reduce_scatter(gid, a, nlanes, current_stream(c.device()));
+}
+
+// ------------------------------------------------------------------ all-reduce (in place)
+void all_reduce(Comm& c, int gid, std::vector<at::Tensor> ts, int algo, int nlanes, double scale) {
+  const LocalList l = local_list(c, gid, ts.size(), "all_reduce tensors");
+  const int dev = c.device();
+  c10::cuda::CUDAGuard guard(dev);
+  for (int i = 0; i < l.n; ++i) {
+    check_tensor(ts[i], "tensor", dev);
+    TORCH_CHECK(ts[i].numel() == ts[0].numel() && ts[i].scalar_type() == ts[0].scalar_type(),
+                "all ranks must pass tensors of the same size and dtype");
+  }
+  const int dt = to_dtype(ts[0].scalar_type());
+  const uint64_t n = (uint64_t)ts[0].numel(), s = dtype_size(dt);
+  if (n == 0) return;
+  cudaStream_t stream = current_stream(dev);
+  const int64_t off = symmetric_offset(c, gid, l, ts);
+  AllReduceArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.algo = algo == kMultimem ? kMultimem : kDirect;
+  a.dtype = dt;
+  a.scale = (float)scale;
+  if (off >= 0) {
+    if (a.algo == kMultimem) TORCH_CHECK(off % 16 == 0 && (n * s) % 16 == 0, "multimem all-reduce needs 16-byte aligned data");
+    a.buf_off = (uint64_t)off;
+    a.elems = n;
+    c.all_reduce(gid, a, nlanes, stream);
+    return;
+  }
+  const uint64_t cap = c.staging_bytes() / s / 8 * 8;
+  TORCH_CHECK(cap > 0, "no staging area configured for non-symmetric tensors");
+  for (uint64_t e0 = 0; e0 < n; e0 += cap) {
+    const uint64_t len = std::min(cap, n - e0);
+    if (a.algo == kMultimem && (len * s) % 16 != 0) a.algo = kDirect;
+    a.buf_off = c.staging_off();
+    a.elems = len;
+    for (int i = 0; i < l.n; ++i) a.data[i] = (char*)ts[i].data_ptr() + e0 * s;
+    c.all_reduce(gid, a, nlanes, stream);
+  }
+}
+
+// ------------------------------------------------------------------ broadcast
+void broadcast(Comm& c, int gid, std::vector<at::Tensor> ts, int root, int nlanes, bool use_multimem) {
+  const LocalList l = local_list(c, gid, ts.size(), "broadcast tensors");
+  const int dev = c.device();
+  c10::cuda::CUDAGuard guard(dev);
+  for (int i = 0; i < l.n; ++i) {
+    check_tensor(ts[i], "tensor", dev);
+    TORCH_CHECK(ts[i].nbytes() == ts[0].nbytes(), "all ranks must pass tensors of the same size");
+  }
+  const uint64_t n = (uint64_t)ts[0].nbytes();
+  if (n == 0) return;
+  cudaStream_t stream = current_stream(dev);
+  const int64_t off = symmetric_offset(c, gid, l, ts);
+  BroadcastArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.root = root;
+  a.use_multimem = use_multimem && c.has_multimem() ? 1 : 0;
+  if (off >= 0) {
+    if (a.use_multimem && (off % 16 != 0 || n % 16 != 0)) a.use_multimem = 0;
+    a.buf_off = (uint64_t)off;
+    a.bytes = n;
+    c.broadcast(gid, a, nlanes, stream);
+    return;
+  }
+  const uint64_t cap = c.staging_bytes() / 16 * 16;
+  TORCH_CHECK(cap > 0, "no staging area configured for non-symmetric tensors");
+  for (uint64_t e0 = 0; e0 < n; e0 += cap) {
+    const uint64_t len = std::min(cap, n - e0);
+    BroadcastArgs b = a;
+    if (b.use_multimem && (len % 16 != 0 || ((uint64_t)ts[0].data_ptr() + e0) % 16 != 0)) b.use_multimem = 0;
+    b.buf_off = c.staging_off();
+    b.bytes = len;
+    for (int i = 0; i < l.n; ++i) b.data[i] = (char*)ts[i].data_ptr() + e0;
+    c.broadcast(gid, b, nlanes, stream);
+  }
+}
+
+at::Tensor heap_tensor(Comm& c, int64_t off, int64_t numel, at::ScalarType dtype, int world_rank) {
+  TORCH_CHECK(off >= 0 && (uint64_t)off + (uint64_t)numel * c10::elementSize(dtype) <= c.heap_bytes(),
+              "range outside the symmetric heap");
+  void* p = (void*)(c.heap_base(world_rank) + (uint64_t)off);
+  auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, c.device());
+  return at::from_blob(p, {numel}, opts);
+}
+
+// Tensors that own a heap block: the block returns to the allocator when the last of them
+// (views included, since they share the storage) is destroyed.
+struct HeapBlock {
+  std::shared_ptr<Comm> comm;
+  int64_t off;
+  ~HeapBlock() {
+    try {
+      comm->free(off);
+    } catch (...) {
+    }
+  }
+};
+
+std::vector<at::Tensor> owned_tensors(std::shared_ptr<Comm> c, int64_t off, int64_t numel, at::ScalarType dtype,
+                                      std::vector<int> owners) {
+  TORCH_CHECK(off >= 0 && (uint64_t)off + (uint64_t)numel * c10::elementSize(dtype) <= c->heap_bytes(),
+              "range outside the symmetric heap");
+  auto blk = std::make_shared<HeapBlock>(HeapBlock{c, off});
+  auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, c->device());
+  std::vector<at::Tensor> out;
+  for (int r : owners) {
+    void* p = (void*)(c->heap_base(r) + (uint64_t)off);
+    out.push_back(at::from_blob(p, {numel}, [blk](void*) {}, opts));
+  }
+  return out;
+}
+
+py::dict status_dict(Comm& c, int li) {
+  const Status s = c.status(li);
+  py::dict d;
+  d["code"] = s.code;
+  d["epoch"] = s.epoch;
+  d["rank"] = s.rank;
+  d["peer"] = s.peer;
+  d["lane"] = s.lane;
+  d["slot_kind"] = s.slot_kind;
+  d["seen"] = s.seen;
+  d["collective"] = s.collective;
+  return d;
+}
+
+}  // namespace
+
+void bind_gemm(py::module_& m);   // gemm_bindings.cpp
+void bind_optim(py::module_& m);  // optim_bindings.cpp
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "pccl native layer: sm_100a collective kernels, symmetric heap, tcgen05 GEMMs";
+  py::register_exception<pccl::Error>(m, "Error", PyExc_RuntimeError);
+
+  m.attr("MAX_RANKS") = kMaxRanks;
+  m.attr("MAX_LANES") = kMaxLanes;
+  m.attr("REGION_BYTES") = kRegionBytes;
+  m.attr("DIRECT") = (int)kDirect;
+  m.attr("RING") = (int)kRing;
+  m.attr("RECURSIVE") = (int)kRecursive;
+  m.attr("PULL") = (int)kPull;
+  m.attr("MULTIMEM") = (int)kMultimem;
+  m.attr("STATUS_OK") = (int)kStatusOk;
+  m.attr("STATUS_TIMEOUT") = (int)kStatusTimeout;
+  m.attr("STATUS_POISONED") = (int)kStatusPoisoned;
+
+  m.def("num_steps", [](int algo, int P) { return num_steps(algo, P); });
+  m.def("ag_step", [](int algo, int P, int r, int t) { return step_tuple(ag_step(algo, P, r, t)); });
+  m.def("rs_step", [](int algo, int P, int r, int t) { return step_tuple(rs_step(algo, P, r, t)); });
+  m.def("rs_stage_offset", [](int algo, int P, int t) { return rs_stage_offset(algo, P, t); });
+  m.def("rs_dep_mask", [](int algo, int P, int t) { return rs_dep_mask(algo, P, t); });
+  m.def("slot_index", [](int lane, int kind, int src) { return slot_index(lane, kind, src); });
+
+  py::class_<IpcSegment>(m, "IpcSegment")
+      .def(py::init<int, uint64_t>(), py::arg("device"), py::arg("bytes"))
+      .def(py::init([](int device, py::bytes handle, uint64_t bytes) {
+             return new IpcSegment(device, std::string(handle), bytes);
+           }),
+           py::arg("device"), py::arg("handle"), py::arg("bytes"))
+      .def_property_readonly("ptr", &IpcSegment::ptr)
+      .def_property_readonly("bytes", &IpcSegment::bytes)
+      .def("handle", [](IpcSegment& s) { return py::bytes(s.handle()); })
+      .def("close", &IpcSegment::close);
+
+  py::class_<VmmSegment>(m, "VmmSegment")
+      .def(py::init<int, uint64_t, int>(), py::arg("device"), py::arg("bytes"), py::arg("world_for_multicast") = 0)
+      .def(py::init<int, int, uint64_t>(), py::arg("device"), py::arg("fd"), py::arg("bytes"))
+      .def_property_readonly("ptr", &VmmSegment::ptr)
+      .def_property_readonly("bytes", &VmmSegment::bytes)
+      .def("export_fd", &VmmSegment::export_fd)
+      .def_static("multicast_supported", &VmmSegment::multicast_supported)
+      .def("multicast_create", &VmmSegment::multicast_create)
+      .def("multicast_import", &VmmSegment::multicast_import)
+      .def("multicast_add_device", &VmmSegment::multicast_add_device)
+      .def("multicast_bind_and_map", &VmmSegment::multicast_bind_and_map)
+      .def("multicast_release", &VmmSegment::multicast_release)
+      .def("close", &VmmSegment::close);
+
+  py::class_<Comm, std::shared_ptr<Comm>>(m, "Comm")
+      .def(py::init<int, int, int, int, std::vector<uint64_t>, std::vector<uint64_t>, uint64_t, uint64_t, uint64_t, uint64_t>(),
+           py::arg("world"), py::arg("rank"), py::arg("nlocal"), py::arg("device"), py::arg("heaps"), py::arg("sigs"),
+           py::arg("mc_heap"), py::arg("heap_bytes"), py::arg("sig_bytes"), py::arg("staging_bytes"))
+      .def_property_readonly("world", &Comm::world)
+      .def_property_readonly("rank", &Comm::rank)
+      .def_property_readonly("nlocal", &Comm::nlocal)
+      .def_property_readonly("device", &Comm::device)
+      .def_property_readonly("has_multimem", &Comm::has_multimem)
+      .def_property_readonly("heap_bytes", &Comm::heap_bytes)
+      .def_property_readonly("heap_used", &Comm::heap_used)
+      .def_property_readonly("staging_off", &Comm::staging_off)
+      .def_property_readonly("staging_bytes", &Comm::staging_bytes)
+      .def_property_readonly("max_lanes", &Comm::max_lanes)
+      .def_property_readonly("kernels_launched", &Comm::kernels_launched)
+      .def("heap_base", &Comm::heap_base)
+      .def("alloc", &Comm::alloc, py::arg("bytes"), py::arg("align") = 256)
+      .def("free", &Comm::free)
+      .def("offset_of", &Comm::offset_of)
+      .def("tensor", &heap_tensor, py::arg("off"), py::arg("numel"), py::arg("dtype"), py::arg("world_rank"))
+      .def("owned_tensors", &owned_tensors)
+      .def("new_group", &Comm::new_group)
+      .def("group_size", &Comm::group_size)
+      .def("group_rank", &Comm::group_rank)
+      .def("set_timeout_ms", &Comm::set_timeout_ms)
+      .def("timeout_ms", &Comm::timeout_ms)
+      .def("status", &status_dict, py::arg("local_slot") = 0)
+      .def("poisoned", &Comm::poisoned)
+      .def("reset_after_failure", &Comm::reset_after_failure)
+      .def("all_gather", &all_gather, py::arg("gid"), py::arg("outs"), py::arg("ins"), py::arg("algo"), py::arg("nlanes"))
+      .def("all_gather_raw", &all_gather_raw)
+      .def("reduce_scatter", &reduce_scatter, py::arg("gid"), py::arg("outs"), py::arg("ins"), py::arg("algo"),
+           py::arg("nlanes"), py::arg("scale") = 1.0, py::arg("wire_dtype") = py::none())
+      .def("reduce_scatter_raw", &reduce_scatter_raw)
+      .def("all_reduce", &all_reduce, py::arg("gid"), py::arg("tensors"), py::arg("algo"), py::arg("nlanes"),
+           py::arg("scale") = 1.0)
+      .def("broadcast", &broadcast, py::arg("gid"), py::arg("tensors"), py::arg("root"), py::arg("nlanes"),
+           py::arg("use_multimem") = false)
+      .def("barrier", [](Comm& c, int gid) {
+        c10::cuda::CUDAGuard guard(c.device());
+        c.barrier(gid, current_stream(c.device()));
+      });
+
+  bind_gemm(m);
+  bind_optim(m);
+}

@@ -1,0 +1,422 @@
+// Device-side building blocks of the collective kernels: system-scope flags with bounded
+// waits, CTA-wide copies to and from peer memory, fp32-accumulating reductions and the
+// NVLS multimem wrappers.
+//
+// Memory-ordering contract used throughout:
+//   producer:  data stores (weak)  ->  bar.sync  ->  fence.acq_rel.sys + st.release.sys flag
+//   consumer:  ld.acquire.sys flag (one thread)  ->  bar.sync  ->  data loads
+// Flags and peer data are never read through the non-coherent (.nc) path.
+// Flags carry the call number (epoch) of the group, so they are never reset and a rank
+// that runs ahead by one call cannot be mistaken for the current one.
+//
+// The reference gets ordering from a host-side cudaEventSynchronize before every
+// MPI_Sendrecv (pccl/src/all_gather.cpp:57-63); here nothing leaves the device.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "device_types.h"
+
+namespace pccl {
+
+constexpr int kCollThreads = 512;
+
+// ---------------------------------------------------------------- raw accessors
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// 16-byte load that bypasses L1: used for memory that another GPU may have written.
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_v4(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st_v4(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+
+// ---------------------------------------------------------------- status / failure
+__device__ __forceinline__ void report_failure(const GroupDev& g, int li, uint32_t code, uint32_t coll,
+                                               int me, int peer, int lane, int kind, uint32_t seen) {
+  Status* st = g.status[li];
+  if (st != nullptr && atomicCAS(&st->code, (uint32_t)kStatusOk, code) == kStatusOk) {
+    st->epoch = g.epoch;
+    st->rank = me;
+    st->peer = peer;
+    st->lane = lane;
+    st->slot_kind = kind;
+    st->seen = seen;
+    st->collective = coll;
+    __threadfence_system();
+  }
+  if (g.poison[li] != nullptr) atomicExch(g.poison[li], 1u);
+}
+
+// One thread spins until flag >= epoch (wrap-safe), the budget runs out, or the
+// communicator is poisoned.  Never traps, never spins without a limit.
+__device__ __forceinline__ bool spin_until(const uint32_t* flag, uint32_t epoch, const GroupDev& g, int li,
+                                           uint32_t* seen_out) {
+  uint32_t v = ld_acquire_sys(flag);
+  if ((int32_t)(v - epoch) >= 0) return true;
+  const uint64_t t0 = global_timer_ns();
+  const uint32_t* poison = g.poison[li];
+  uint32_t it = 0;
+  for (;;) {
+    v = ld_acquire_sys(flag);
+    if ((int32_t)(v - epoch) >= 0) return true;
+    if ((++it & 63u) == 0u) {
+      if (poison != nullptr && *reinterpret_cast<const volatile uint32_t*>(poison) != 0u) break;
+      if (global_timer_ns() - t0 > g.timeout_ns) break;
+      __nanosleep(64);
+    }
+  }
+  *seen_out = v;
+  return false;
+}
+
+struct LaneCtx {
+  int li;     // local rank slot (blockIdx.y)
+  int me;     // my group index
+  int lane;   // blockIdx.x
+  uint32_t coll;
+};
+
+// All threads of the CTA call this; thread 0 waits.  Returns false (to all threads) when
+// the wait gave up; the status word then says where.
+__device__ __forceinline__ bool cta_wait(const GroupDev& g, const LaneCtx& c, int kind, int src) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    uint32_t seen = 0;
+    const uint32_t* flag = g.sig[c.me] + slot_index(c.lane, kind, src);
+    bool ok = spin_until(flag, g.epoch, g, c.li, &seen);
+    if (!ok) {
+      const bool poisoned = g.poison[c.li] != nullptr &&
+                            *reinterpret_cast<const volatile uint32_t*>(g.poison[c.li]) != 0u;
+      report_failure(g, c.li, poisoned ? kStatusPoisoned : kStatusTimeout, c.coll, c.me, src, c.lane, kind, seen);
+    }
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  const int ok = s_ok;
+  __syncthreads();
+  return ok != 0;
+}
+
+// Wait for the same slot kind from every member whose bit is set in `mask`.
+__device__ __forceinline__ bool cta_wait_mask(const GroupDev& g, const LaneCtx& c, int kind, unsigned mask) {
+  __shared__ int s_ok_all;
+  if (threadIdx.x == 0) s_ok_all = 1;
+  __syncthreads();
+  if (threadIdx.x < (unsigned)g.size && ((mask >> threadIdx.x) & 1u)) {
+    uint32_t seen = 0;
+    const int src = threadIdx.x;
+    const uint32_t* flag = g.sig[c.me] + slot_index(c.lane, kind, src);
+    if (!spin_until(flag, g.epoch, g, c.li, &seen)) {
+      const bool poisoned = g.poison[c.li] != nullptr &&
+                            *reinterpret_cast<const volatile uint32_t*>(g.poison[c.li]) != 0u;
+      report_failure(g, c.li, poisoned ? kStatusPoisoned : kStatusTimeout, c.coll, c.me, src, c.lane, kind, seen);
+      atomicExch(&s_ok_all, 0);
+    }
+  }
+  __syncthreads();
+  const int ok = s_ok_all;
+  __syncthreads();
+  return ok != 0;
+}
+
+// Publish slot(lane, kind, me) = epoch in the pad of every member in `mask`.
+// The leading bar.sync orders every thread's earlier stores before the release.
+__device__ __forceinline__ void cta_signal_mask(const GroupDev& g, const LaneCtx& c, int kind, unsigned mask) {
+  __syncthreads();
+  if (threadIdx.x < (unsigned)g.size && ((mask >> threadIdx.x) & 1u)) {
+    __threadfence_system();
+    st_release_sys(g.sig[threadIdx.x] + slot_index(c.lane, kind, c.me), g.epoch);
+  }
+}
+__device__ __forceinline__ void cta_signal(const GroupDev& g, const LaneCtx& c, int kind, int dst) {
+  cta_signal_mask(g, c, kind, 1u << dst);
+}
+
+__device__ __forceinline__ unsigned others_mask(int P, int me) { return ((1u << P) - 1u) & ~(1u << me); }
+
+// ---------------------------------------------------------------- lane partition
+// Split `total` bytes/elements into gridDim.x contiguous pieces on `gran` boundaries.
+__device__ __forceinline__ void lane_range(uint64_t total, uint64_t gran, int lane, int nlanes, uint64_t* lo,
+                                           uint64_t* hi) {
+  const uint64_t units = (total + gran - 1) / gran;
+  const uint64_t per = (units + nlanes - 1) / nlanes;
+  uint64_t a = per * lane, b = a + per;
+  if (a > units) a = units;
+  if (b > units) b = units;
+  a *= gran;
+  b *= gran;
+  if (a > total) a = total;
+  if (b > total) b = total;
+  *lo = a;
+  *hi = b;
+}
+
+// ---------------------------------------------------------------- CTA-wide copy
+// REMOTE_SRC: the source may have been written by another GPU during this kernel.
+template <bool REMOTE_SRC>
+__device__ __forceinline__ void cta_copy(char* __restrict__ dst, const char* __restrict__ src, uint64_t n) {
+  if (n == 0 || dst == src) return;
+  const uint64_t tid = threadIdx.x, nt = blockDim.x;
+  const uintptr_t ds = reinterpret_cast<uintptr_t>(dst), ss = reinterpret_cast<uintptr_t>(src);
+  if (((ds ^ ss) & 15u) == 0) {
+    uint64_t head = (16 - (ss & 15u)) & 15u;
+    if (head > n) head = n;
+    for (uint64_t i = tid; i < head; i += nt) dst[i] = src[i];
+    const uint64_t nvec = (n - head) >> 4;
+    const char* s = src + head;
+    char* d = dst + head;
+    constexpr int U = 8;
+    uint64_t i = tid;
+    for (; i + (U - 1) * nt < nvec; i += U * nt) {
+      uint4 v[U];
+#pragma unroll
+      for (int k = 0; k < U; ++k)
+        v[k] = REMOTE_SRC ? ld_volatile_v4(s + ((i + k * nt) << 4)) : ld_v4(s + ((i + k * nt) << 4));
+#pragma unroll
+      for (int k = 0; k < U; ++k) st_v4(d + ((i + k * nt) << 4), v[k]);
+    }
+    for (; i < nvec; i += nt) {
+      uint4 v = REMOTE_SRC ? ld_volatile_v4(s + (i << 4)) : ld_v4(s + (i << 4));
+      st_v4(d + (i << 4), v);
+    }
+    const uint64_t done = head + (nvec << 4);
+    for (uint64_t j = done + tid; j < n; j += nt) dst[j] = src[j];
+  } else if (((ds | ss) & 3u) == 0 && (n & 3u) == 0) {
+    const uint32_t* s = reinterpret_cast<const uint32_t*>(src);
+    uint32_t* d = reinterpret_cast<uint32_t*>(dst);
+    for (uint64_t i = tid; i < (n >> 2); i += nt) d[i] = REMOTE_SRC ? ld_relaxed_sys(s + i) : s[i];
+  } else {
+    const volatile char* s = src;
+    for (uint64_t i = tid; i < n; i += nt) dst[i] = s[i];
+  }
+}
+
+// ---------------------------------------------------------------- typed 8-element vectors
+template <int DT>
+struct Elem;
+template <>
+struct Elem<kBF16> {
+  static constexpr int size = 2;
+  __device__ static __forceinline__ float load1(const char* p) {
+    return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
+  }
+  __device__ static __forceinline__ void store1(char* p, float f) {
+    *reinterpret_cast<__nv_bfloat16*>(p) = __float2bfloat16_rn(f);
+  }
+  __device__ static __forceinline__ void unpack(const uint4& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ static __forceinline__ uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <>
+struct Elem<kF16> {
+  static constexpr int size = 2;
+  __device__ static __forceinline__ float load1(const char* p) {
+    return __half2float(*reinterpret_cast<const __half*>(p));
+  }
+  __device__ static __forceinline__ void store1(char* p, float f) {
+    *reinterpret_cast<__half*>(p) = __float2half_rn(f);
+  }
+  __device__ static __forceinline__ void unpack(const uint4& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+  __device__ static __forceinline__ uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <>
+struct Elem<kF32> {
+  static constexpr int size = 4;
+  __device__ static __forceinline__ float load1(const char* p) { return *reinterpret_cast<const float*>(p); }
+  __device__ static __forceinline__ void store1(char* p, float f) { *reinterpret_cast<float*>(p) = f; }
+};
+
+// Load 8 consecutive elements as fp32.  p must be 16-byte aligned.
+template <int DT, bool REMOTE>
+__device__ __forceinline__ void load8(const char* p, float* f) {
+  if constexpr (DT == kF32) {
+    uint4 a = REMOTE ? ld_volatile_v4(p) : ld_v4(p);
+    uint4 b = REMOTE ? ld_volatile_v4(p + 16) : ld_v4(p + 16);
+    f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+    f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+  } else {
+    uint4 a = REMOTE ? ld_volatile_v4(p) : ld_v4(p);
+    Elem<DT>::unpack(a, f);
+  }
+}
+template <int DT>
+__device__ __forceinline__ void store8(char* p, const float* f) {
+  if constexpr (DT == kF32) {
+    st_v4(p, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
+    st_v4(p + 16, make_uint4(__float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7])));
+  } else {
+    st_v4(p, Elem<DT>::pack(f));
+  }
+}
+template <int DT>
+__device__ __forceinline__ float load_scalar(const char* p) {
+  return Elem<DT>::load1(p);
+}
+
+// ---------------------------------------------------------------- CTA-wide reduction
+// out[i] = cast<TOUT>( scale * ( a[i] + sum_k w[k][i] ) ),  i in [0, count)
+// `a` has TA elements (may be nullptr), the nw extra sources have TW elements; all sums in
+// fp32, one rounding at the store.  REMOTE_W: the w sources may have been written by peers.
+constexpr int kMaxReduceSrc = kMaxRanks;
+
+template <int TOUT>
+__device__ __forceinline__ void store8_all(char* const* outs, int nout, uint64_t byte_off, const float* f) {
+  for (int o = 0; o < nout; ++o) store8<TOUT>(outs[o] + byte_off, f);
+}
+
+// outs: nout destinations that all receive the same result (nout > 1: the broadcast half
+// of an all-reduce).
+template <int TA, int TW, int TOUT, bool REMOTE_W>
+__device__ __forceinline__ void cta_reduce(char* const* outs, int nout, const char* a,
+                                           const char* const* w, int nw, uint64_t count, float scale) {
+  if (count == 0) return;
+  const uint64_t tid = threadIdx.x, nt = blockDim.x;
+  bool aligned = (a == nullptr || (reinterpret_cast<uintptr_t>(a) & 15u) == 0);
+  for (int o = 0; o < nout; ++o) aligned = aligned && (reinterpret_cast<uintptr_t>(outs[o]) & 15u) == 0;
+  for (int k = 0; k < nw; ++k) aligned = aligned && (reinterpret_cast<uintptr_t>(w[k]) & 15u) == 0;
+  uint64_t done = 0;
+  if (aligned) {
+    const uint64_t ngroups = count >> 3;
+    constexpr uint64_t SA = 8 * Elem<TA>::size, SW = 8 * Elem<TW>::size, SO = 8 * Elem<TOUT>::size;
+    uint64_t i = tid;
+    // two groups in flight per thread
+    for (; i + nt < ngroups; i += 2 * nt) {
+      float acc0[8], acc1[8], t0[8], t1[8];
+      if (a != nullptr) {
+        load8<TA, false>(a + i * SA, acc0);
+        load8<TA, false>(a + (i + nt) * SA, acc1);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc0[e] = acc1[e] = 0.f;
+      }
+      for (int k = 0; k < nw; ++k) {
+        load8<TW, REMOTE_W>(w[k] + i * SW, t0);
+        load8<TW, REMOTE_W>(w[k] + (i + nt) * SW, t1);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          acc0[e] += t0[e];
+          acc1[e] += t1[e];
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        acc0[e] *= scale;
+        acc1[e] *= scale;
+      }
+      store8_all<TOUT>(outs, nout, i * SO, acc0);
+      store8_all<TOUT>(outs, nout, (i + nt) * SO, acc1);
+    }
+    for (; i < ngroups; i += nt) {
+      float acc[8], t[8];
+      if (a != nullptr) {
+        load8<TA, false>(a + i * SA, acc);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      }
+      for (int k = 0; k < nw; ++k) {
+        load8<TW, REMOTE_W>(w[k] + i * SW, t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += t[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= scale;
+      store8_all<TOUT>(outs, nout, i * SO, acc);
+    }
+    done = ngroups << 3;
+  }
+  for (uint64_t i = done + tid; i < count; i += nt) {
+    float acc = a != nullptr ? load_scalar<TA>(a + i * Elem<TA>::size) : 0.f;
+    for (int k = 0; k < nw; ++k) {
+      const char* p = w[k] + i * Elem<TW>::size;
+      if constexpr (Elem<TW>::size == 4) {
+        acc += __uint_as_float(REMOTE_W ? ld_relaxed_sys(reinterpret_cast<const uint32_t*>(p))
+                                        : *reinterpret_cast<const uint32_t*>(p));
+      } else {
+        unsigned short bits = *reinterpret_cast<const volatile unsigned short*>(p);
+        if constexpr (TW == kBF16) acc += __uint_as_float(uint32_t(bits) << 16);
+        else acc += __half2float(__ushort_as_half(bits));
+      }
+    }
+    for (int o = 0; o < nout; ++o) Elem<TOUT>::store1(outs[o] + i * Elem<TOUT>::size, acc * scale);
+  }
+}
+
+// ---------------------------------------------------------------- NVLS (multimem) wrappers
+// One instruction addresses the same offset of every GPU bound to the multicast object:
+// ld_reduce sums inside the switch (fp32 accumulation for 16-bit types), st writes all.
+template <int DT>
+__device__ __forceinline__ uint4 multimem_ld_reduce_v4(const char* mc_ptr) {
+  uint4 v;
+  if constexpr (DT == kBF16) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_ptr) : "memory");
+  } else if constexpr (DT == kF16) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_ptr) : "memory");
+  } else {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_ptr) : "memory");
+  }
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(char* mc_ptr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+}  // namespace pccl

@@ -1,0 +1,85 @@
+"""Pick the algorithm variant and the number of lanes for one collective call.
+
+``algorithm="auto"`` consults a table keyed by collective, group size and message size
+that is produced from measured bus bandwidth (``benchmark_raw_collectives`` writes it with
+``--write-tuning-table``).  The reference has no such choice: its caller passes
+``use_rd`` / ``use_rh`` by hand (``pccl/all_gather.py:98-105``) and its README only says
+that the recursive variants are "typically faster at scale".
+
+Environment overrides: ``PCCL_ALGO`` (direct|ring|recursive|pull|multimem) and
+``PCCL_LANES`` (integer) win over the table.
+"""
+from __future__ import annotations
+
+import json
+import os
+from functools import lru_cache
+from pathlib import Path
+from typing import Dict, List, Optional, Tuple
+
+from . import schedule as sch
+
+TABLE_PATH = Path(__file__).resolve().parent / "tuning_table.json"
+
+# Fallback when the table has no row: bytes each lane should at least move, lane ceiling.
+MIN_BYTES_PER_LANE = 32 << 10
+DEFAULT_MAX_LANES = 64
+
+
+@lru_cache(maxsize=1)
+def _table() -> Dict:
+    if TABLE_PATH.exists():
+        try:
+            return json.loads(TABLE_PATH.read_text())
+        except (OSError, ValueError):
+            return {}
+    return {}
+
+
+def reload_table() -> None:
+    _table.cache_clear()
+
+
+def default_lanes(nbytes: int, max_lanes: int = DEFAULT_MAX_LANES) -> int:
+    lanes = max(1, min(max_lanes, nbytes // MIN_BYTES_PER_LANE))
+    return int(lanes)
+
+
+def lookup(collective: str, world: int, nbytes: int) -> Optional[Tuple[str, int]]:
+    rows: List = _table().get(collective, {}).get(str(world), [])
+    for max_bytes, algo, lanes in rows:
+        if max_bytes is None or nbytes <= max_bytes:
+            return algo, int(lanes)
+    return None
+
+
+def choose(collective: str, world: int, nbytes: int, *, requested: str = sch.AUTO, symmetric_in: bool = False,
+           symmetric_out: bool = False, has_multimem: bool = False, lanes: Optional[int] = None,
+           max_lanes: int = DEFAULT_MAX_LANES) -> Tuple[str, int]:
+    """Return ``(algorithm, nlanes)``.  ``nbytes`` is the per-rank block size."""
+    env_algo = os.environ.get("PCCL_ALGO")
+    env_lanes = os.environ.get("PCCL_LANES")
+    algo = requested
+    if algo == sch.AUTO and env_algo:
+        algo = env_algo
+    picked_lanes = None
+    if algo == sch.AUTO:
+        hit = lookup(collective, world, nbytes)
+        if hit is not None:
+            algo, picked_lanes = hit
+        else:
+            algo = sch.DIRECT
+    # Variants that read or multicast peer memory need the right tensors in the heap.
+    if algo == sch.MULTIMEM and not has_multimem:
+        algo = sch.DIRECT
+    if collective == "reduce_scatter" and algo in (sch.PULL, sch.MULTIMEM) and not symmetric_in:
+        algo = sch.DIRECT
+    if collective == "all_gather" and algo == sch.MULTIMEM and (nbytes % 16 != 0):
+        algo = sch.DIRECT
+    if algo == sch.RECURSIVE and not sch.is_pow2(world):
+        if requested == sch.RECURSIVE:
+            sch.check_algo(algo, world)   # raises: the caller asked for it explicitly
+        algo = sch.DIRECT
+    if lanes is None:
+        lanes = int(env_lanes) if env_lanes else (picked_lanes or default_lanes(nbytes, max_lanes))
+    return algo, max(1, min(int(lanes), max_lanes))

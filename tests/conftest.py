@@ -1,0 +1,42 @@
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: test needs a CUDA device (run with -m gpu on a B200)")
+    config.addinivalue_line("markers", "multigpu: test needs at least two CUDA devices")
+
+
+def free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.fixture
+def port():
+    return free_port()
+
+
+def pytest_collection_modifyitems(config, items):
+    try:
+        import torch
+
+        ngpu = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    except Exception:
+        ngpu = 0
+    skip_gpu = pytest.mark.skip(reason="needs a CUDA device")
+    skip_multi = pytest.mark.skip(reason="needs at least two CUDA devices")
+    for item in items:
+        if "gpu" in item.keywords and ngpu == 0:
+            item.add_marker(skip_gpu)
+        if "multigpu" in item.keywords and ngpu < 2:
+            item.add_marker(skip_multi)

@@ -1,0 +1,160 @@
+"""World-size-2..4 collectives on CPU over gloo, checked against torch.distributed.
+
+Covers the first benchmark configuration: 1,048,576 fp32 elements per rank drawn N(0,1)
+from seed+rank, ring and recursive algorithms, compared with the torch.distributed result.
+"""
+import pytest
+import torch
+import torch.distributed as dist
+
+from tests._mp import run_ranks
+
+
+def _config1(rank, world, n):
+    import pccl
+
+    comm = pccl.init()
+    g = comm.world_group
+    assert not g.native
+    gen = torch.Generator().manual_seed(1234 + rank)
+    x = torch.randn(n, generator=gen, dtype=torch.float32)
+    for algo in ("ring", "recursive", "direct"):
+        out = torch.empty(world * n)
+        gold = torch.empty(world * n)
+        pccl._all_gather(out, x, g, use_rd=(algo == "recursive"), algorithm=None if algo != "direct" else "direct")
+        pccl._all_gather(gold, x, None)
+        assert torch.equal(out, gold), f"all_gather {algo} differs from torch.distributed"
+
+        big = torch.randn(world * n, generator=gen, dtype=torch.float32)
+        out = torch.empty(n)
+        gold = torch.empty(n)
+        pccl._reduce_scatter(out, big, g, use_rh=(algo == "recursive"), algorithm=None if algo != "direct" else "direct")
+        pccl._reduce_scatter(gold, big, None)
+        if world == 2:
+            assert torch.equal(out, gold)          # one addition: exact
+        else:
+            torch.testing.assert_close(out, gold, rtol=1e-5, atol=1e-6)
+
+        t = torch.randn(n + 3, generator=gen)
+        ref = t.clone()
+        pccl._all_reduce(t, g, use_rh_and_rd=(algo == "recursive"))
+        dist.all_reduce(ref)
+        torch.testing.assert_close(t, ref, rtol=1e-5, atol=1e-6)
+    # exported reference names
+    out = torch.empty(world * n)
+    pccl.recursive_doubling_allgather_mpi(out, x, g)
+    gold = torch.empty(world * n)
+    dist.all_gather_into_tensor(gold, x)
+    assert torch.equal(out, gold)
+    big = torch.randn(world * n, generator=gen)
+    o1, o2, gold = torch.empty(n), torch.empty(n), torch.empty(n)
+    pccl.recursive_halving_reduce_scatter_mpi(o1, big, g)
+    pccl.ring_reduce_scatter_mpi(o2, big, g)
+    dist.reduce_scatter_tensor(gold, big)
+    torch.testing.assert_close(o1, gold, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(o2, gold, rtol=1e-5, atol=1e-6)
+
+
+def test_config1_world2_one_mebi_elements(port):
+    run_ranks(_config1, 2, port, args=(1 << 20,))
+
+
+def test_world4_small(port):
+    run_ranks(_config1, 4, port, args=(1000,))
+
+
+def _bf16_and_scale(rank, world):
+    import pccl
+
+    g = pccl.init().world_group
+    gen = torch.Generator().manual_seed(7 + rank)
+    n = 515
+    big = torch.randn(world * n, generator=gen).to(torch.bfloat16)
+    allin = [torch.empty_like(big) for _ in range(world)]
+    dist.all_gather(allin, big)
+    want = sum(t.float() for t in allin).view(world, n)[rank] / world
+    for algo in ("ring", "direct"):
+        out = torch.empty(n, dtype=torch.float32)
+        pccl._reduce_scatter(out, big, g, algorithm=algo, scale=1.0 / world, wire_dtype=torch.float32)
+        torch.testing.assert_close(out, want, rtol=1e-6, atol=1e-6)   # fp32 wire: only reassociation
+        out16 = torch.empty(n, dtype=torch.bfloat16)
+        pccl._reduce_scatter(out16, big, g, algorithm=algo, scale=1.0 / world)
+        torch.testing.assert_close(out16.float(), want, rtol=2e-2, atol=2e-2)
+    t = torch.full((10,), float(rank + 1))
+    pccl.broadcast(t, 1, g)
+    assert torch.equal(t, torch.full((10,), 2.0))
+    pccl.barrier(g)
+    req = pccl._all_gather(torch.empty(world * 4), torch.ones(4), g, async_op=True)
+    assert isinstance(req, pccl.Request)
+    seen = []
+    req.wait(lambda: seen.append(1))
+    assert seen == [1]
+
+
+def test_bf16_scale_broadcast_barrier_world3(port):
+    run_ranks(_bf16_and_scale, 3, port)
+
+
+def _two_d(rank, world):
+    import pccl
+
+    pgs = pccl.ProcessGroups(2, 2)
+    assert pgs.get_world_size() == [2, 2]
+    assert pgs.get_rank() == [rank % 2, (rank // 2) % 2]
+    assert pgs.get_rank(0) == rank % 2 and pgs.get_world_size(1) == 2
+    with pytest.raises(ValueError):
+        pgs.get_rank(2)
+    assert pgs.get_inner_group().ranks == [rank - rank % 2, rank - rank % 2 + 1]
+    assert pgs.get_outer_group().ranks == [rank % 2, rank % 2 + 2]
+    n = 37
+    x = torch.arange(n, dtype=torch.float32) + 100 * rank
+    out = torch.empty(world * n)
+    pccl.all_gather_2D(out, x, pgs, use_rd=True)
+    gold = torch.empty(world * n)
+    dist.all_gather_into_tensor(gold, x)
+    assert torch.equal(out, gold)
+    big = torch.randn(world * n, generator=torch.Generator().manual_seed(rank))
+    o = torch.empty(n)
+    pccl.reduce_scatter_2D(o, big, pgs, use_rh=True)
+    gold = torch.empty(n)
+    dist.reduce_scatter_tensor(gold, big)
+    torch.testing.assert_close(o, gold, rtol=1e-5, atol=1e-6)
+    # mixed backends: torch groups inside, library groups outside
+    mixed = pccl.ProcessGroups(2, 2, inner_group_backend="gloo", outer_group_backend="pccl")
+    out2 = torch.empty(world * n)
+    pccl.all_gather_2D(out2, x, mixed, use_rd=True)
+    assert torch.equal(out2, gold.new_tensor(out))
+    with pytest.raises(ValueError):
+        pccl.ProcessGroups(3, 1)
+    with pytest.raises(ValueError):
+        pccl.ProcessGroups(2, 2, inner_group_backend="smoke-signals")
+    # two independent grids of 2 ranks
+    pair = pccl.ProcessGroups(2, 1)
+    assert pair.num_2d_grids == 2
+    o = torch.empty(2 * n)
+    pccl.all_gather_2D(o, x, pair)
+    base = rank - rank % 2
+    assert torch.equal(o[:n], torch.arange(n, dtype=torch.float32) + 100 * base)
+
+
+def test_process_groups_and_2d_world4(port):
+    run_ranks(_two_d, 4, port)
+
+
+def _dead_peer(rank, world):
+    """A rank that never joins a step must surface as PcclTimeoutError on its peer."""
+    import os
+
+    os.environ["PCCL_P2P_TIMEOUT_S"] = "2"
+    import pccl
+
+    g = pccl.init().world_group
+    if rank == 1:
+        return                      # leaves between steps: never posts its send/recv
+    out = torch.empty(world * 8)
+    with pytest.raises(pccl.PcclTimeoutError):
+        pccl._all_gather(out, torch.ones(8), g)
+
+
+def test_missing_rank_times_out(port):
+    run_ranks(_dead_peer, 2, port)
