@@ -140,11 +140,23 @@ def _all_gather_2d_native(out, inp, inner: Group, outer: Group, intra: int, inte
     a2 = sch.DIRECT if a2 in (sch.PULL, sch.MULTIMEM) else a2
 
     def launch():
-        # outer level: member o' of my column lands at block o'*intra + i
-        native.all_gather_raw(outer.gid, sch.ALGO_IDS[a1], l1, [inp.data_ptr()], [0], recv_off + i * n,
-                              0, 0, intra * n, 0, n, n, 1, 0)
-        # inner level, in place: member i' contributes the `inter` blocks o'*intra + i'
-        native.all_gather_raw(inner.gid, sch.ALGO_IDS[a2], l2, [0], [out_ptr], recv_off,
-                              n, intra * n, n, intra * n, n, n, inter, 0)
+        ag2d_outer_call(native, outer.gid, sch.ALGO_IDS[a1], l1, [inp.data_ptr()], recv_off, i, n, intra)
+        ag2d_inner_call(native, inner.gid, sch.ALGO_IDS[a2], l2, [out_ptr], recv_off, n, intra, inter)
 
     return run_native(inner, async_op, launch)
+
+
+def ag2d_outer_call(native, gid: int, algo_id: int, lanes: int, in_ptrs, recv_off: int, inner_index: int, n: int,
+                    intra: int) -> None:
+    """Outer level of the 2-D all-gather: member o' of column ``inner_index`` lands at block
+    ``o'*intra + inner_index`` of the landing zone."""
+    native.all_gather_raw(gid, algo_id, lanes, list(in_ptrs), [0] * len(in_ptrs), recv_off + inner_index * n,
+                          0, 0, intra * n, 0, n, n, 1, 0)
+
+
+def ag2d_inner_call(native, gid: int, algo_id: int, lanes: int, out_ptrs, recv_off: int, n: int, intra: int,
+                    inter: int) -> None:
+    """Inner level, in place: member i' contributes the ``inter`` blocks ``o'*intra + i'``;
+    a non-zero ``out_ptrs`` entry receives the whole result in global-rank order."""
+    native.all_gather_raw(gid, algo_id, lanes, [0] * len(out_ptrs), list(out_ptrs), recv_off,
+                          n, intra * n, n, intra * n, n, n, inter, 0)

@@ -99,6 +99,12 @@ def build(verbose: bool = False, force: bool = False):
         from torch.utils import cpp_extension
 
         BUILD_DIR.mkdir(exist_ok=True)
+        # A toolchain that only ships a static libstdc++ gives the extension its own,
+        # never-initialised copy of the iostream locale (integer formatting then crashes).
+        # The distribution compiler links the shared libstdc++ that torch itself uses.
+        for var, path in (("CXX", "/usr/bin/g++"), ("CC", "/usr/bin/gcc")):
+            if os.path.exists(path) and os.environ.get("PCCL_KEEP_COMPILER") != "1":
+                os.environ[var] = path
         cuda_home = cpp_extension.CUDA_HOME
         if cuda_home is None or not (Path(cuda_home) / "bin" / "nvcc").exists():
             raise RuntimeError("pccl: nvcc not found; the native extension cannot be built on this machine")

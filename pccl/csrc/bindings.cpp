@@ -64,7 +64,7 @@ int64_t symmetric_offset(Comm& c, int gid, const LocalList& l, const std::vector
     const int owner = gs.ranks[l.first + i];
     const int64_t o = c.offset_of((uint64_t)ts[i].data_ptr(), (uint64_t)ts[i].nbytes(), owner);
     if (off == -2) off = o;
-    TORCH_CHECK(o == off, "tensors of the emulated ranks are not at the same heap offset");
+    if (o != off) return -1;   // emulated ranks at different offsets: treat as private memory
   }
   return off;
 }
@@ -370,6 +370,9 @@ at::Tensor heap_tensor(Comm& c, int64_t off, int64_t numel, at::ScalarType dtype
 struct HeapBlock {
   std::shared_ptr<Comm> comm;
   int64_t off;
+  HeapBlock(std::shared_ptr<Comm> c, int64_t o) : comm(std::move(c)), off(o) {}
+  HeapBlock(const HeapBlock&) = delete;
+  HeapBlock& operator=(const HeapBlock&) = delete;
   ~HeapBlock() {
     try {
       comm->free(off);
@@ -382,7 +385,7 @@ std::vector<at::Tensor> owned_tensors(std::shared_ptr<Comm> c, int64_t off, int6
                                       std::vector<int> owners) {
   TORCH_CHECK(off >= 0 && (uint64_t)off + (uint64_t)numel * c10::elementSize(dtype) <= c->heap_bytes(),
               "range outside the symmetric heap");
-  auto blk = std::make_shared<HeapBlock>(HeapBlock{c, off});
+  auto blk = std::make_shared<HeapBlock>(c, off);
   auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, c->device());
   std::vector<at::Tensor> out;
   for (int r : owners) {
@@ -427,6 +430,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("STATUS_TIMEOUT") = (int)kStatusTimeout;
   m.attr("STATUS_POISONED") = (int)kStatusPoisoned;
 
+  m.def("_throw_test", [](int k) {
+    if (k == 0) throw pccl::Error("pccl error");
+    if (k == 1) TORCH_CHECK(false, "torch check");
+    if (k == 2) throw std::runtime_error("runtime error");
+  });
   m.def("num_steps", [](int algo, int P) { return num_steps(algo, P); });
   m.def("ag_step", [](int algo, int P, int r, int t) { return step_tuple(ag_step(algo, P, r, t)); });
   m.def("rs_step", [](int algo, int P, int r, int t) { return step_tuple(rs_step(algo, P, r, t)); });

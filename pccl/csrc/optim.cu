@@ -1,0 +1,189 @@
+// Elementwise training kernels of the ZeRO-3 engine: fused AdamW on a parameter shard,
+// squared-norm partial sums for gradient clipping, and softmax cross-entropy computed
+// forward and backward in one pass over the logits.
+//
+// The reference contains none of this (it hooks DeepSpeed, pccl/patch_deepspeed.py:95-126,
+// and DeepSpeed brings its own optimizer); they exist here because the engine that stands
+// in for DeepSpeed has to do the optimizer step inside the timed region.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "optim.h"
+
+namespace pccl {
+
+namespace {
+
+constexpr int kOptThreads = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <bool MAX>
+__device__ __forceinline__ float block_reduce(float v, float* smem) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = MAX ? warp_max(v) : warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = MAX ? -INFINITY : 0.f;
+  for (int i = 0; i < nw; ++i) r = MAX ? fmaxf(r, smem[i]) : r + smem[i];
+  return r;
+}
+
+// ---------------------------------------------------------------- squared norm
+// Grid-stride partial sums, one atomicAdd per block into *out (zeroed by the caller).
+template <typename T>
+__global__ void __launch_bounds__(kOptThreads) sq_norm_kernel(const T* __restrict__ x, uint64_t n, float* out) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    const float v = (float)x[i];
+    acc += v * v;
+  }
+  acc = block_reduce<false>(acc, red);
+  if (threadIdx.x == 0) atomicAdd(out, acc);
+}
+
+// ---------------------------------------------------------------- AdamW
+// One pass over the shard: reads grad, master, m, v; writes master, m, v and the bf16
+// working copy that the next all-gather sends out.  total_sq_norm (device scalar, may be
+// null) holds the squared global gradient norm; the clip factor is derived on the device,
+// so no host synchronisation sits between the norm all-reduce and the update.
+template <typename G>
+__global__ void __launch_bounds__(kOptThreads)
+    adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, const G* __restrict__ grad,
+                 __nv_bfloat16* __restrict__ param, uint64_t n, AdamWArgs a, const float* total_sq_norm) {
+  float clip = 1.0f;
+  if (total_sq_norm != nullptr && a.max_grad_norm > 0.f) {
+    const float norm = sqrtf(*total_sq_norm) * a.grad_scale;
+    clip = fminf(1.0f, a.max_grad_norm / (norm + 1e-6f));
+  }
+  const float gs = a.grad_scale * clip;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    const float g = (float)grad[i] * gs;
+    float p = master[i];
+    float mi = a.beta1 * m[i] + (1.f - a.beta1) * g;
+    float vi = a.beta2 * v[i] + (1.f - a.beta2) * g * g;
+    const float mhat = mi * a.bias1, vhat = vi * a.bias2;
+    p = p * (1.f - a.lr * a.weight_decay) - a.lr * mhat / (sqrtf(vhat) + a.eps);
+    master[i] = p;
+    m[i] = mi;
+    v[i] = vi;
+    param[i] = __float2bfloat16_rn(p);
+  }
+}
+
+// ---------------------------------------------------------------- softmax cross-entropy, fwd + bwd
+// One CTA per row.  The row of logits is read from HBM once into shared memory, reduced
+// (max, sum of exponentials), and overwritten in place with d(loss)/d(logits) =
+// (softmax - onehot) * grad_scale.  loss_sum accumulates the per-row losses.
+__global__ void __launch_bounds__(512) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
+                                                         float* loss_sum, int vocab, int64_t row_stride, float grad_scale,
+                                                         int64_t ignore_index) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* row_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __shared__ float red[32];
+  __nv_bfloat16* row = logits + (int64_t)blockIdx.x * row_stride;
+  const int64_t tgt = targets[blockIdx.x];
+  const int nvec = vocab >> 3;  // 8 bf16 = 16 bytes (row_stride and vocab are multiples of 8)
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 q = reinterpret_cast<const uint4*>(row)[i];
+    reinterpret_cast<uint4*>(row_s)[i] = q;
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      mx = fmaxf(mx, fmaxf(f.x, f.y));
+    }
+  }
+  for (int i = (nvec << 3) + threadIdx.x; i < vocab; i += blockDim.x) {
+    row_s[i] = row[i];
+    mx = fmaxf(mx, __bfloat162float(row[i]));
+  }
+  mx = block_reduce<true>(mx, red);
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += __expf(__bfloat162float(row_s[i]) - mx);
+  sum = block_reduce<false>(sum, red);
+  const bool ignored = tgt == ignore_index;
+  if (threadIdx.x == 0 && !ignored) {
+    const float lt = __bfloat162float(row_s[tgt]);
+    atomicAdd(loss_sum, (mx + logf(sum) - lt));
+  }
+  const float inv = ignored ? 0.f : grad_scale / sum;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    uint4 q = reinterpret_cast<const uint4*>(row_s)[i];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 f = __bfloat1622float2(h[k]);
+      const int c = (i << 3) + 2 * k;
+      f.x = __expf(f.x - mx) * inv - ((c == tgt && !ignored) ? grad_scale : 0.f);
+      f.y = __expf(f.y - mx) * inv - ((c + 1 == tgt && !ignored) ? grad_scale : 0.f);
+      h[k] = __floats2bfloat162_rn(f.x, f.y);
+    }
+    reinterpret_cast<uint4*>(row)[i] = q;
+  }
+  for (int i = (nvec << 3) + threadIdx.x; i < vocab; i += blockDim.x) {
+    const float p = __expf(__bfloat162float(row_s[i]) - mx) * inv - ((i == tgt && !ignored) ? grad_scale : 0.f);
+    row[i] = __float2bfloat16_rn(p);
+  }
+}
+
+int grid_for(uint64_t n, int threads, int per_thread) {
+  uint64_t blocks = (n + (uint64_t)threads * per_thread - 1) / ((uint64_t)threads * per_thread);
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return (int)blocks;
+}
+
+}  // namespace
+
+cudaError_t launch_sq_norm(const void* x, int dtype_is_bf16, uint64_t n, float* out, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  const int grid = grid_for(n, kOptThreads, 16);
+  if (dtype_is_bf16) sq_norm_kernel<<<grid, kOptThreads, 0, s>>>((const __nv_bfloat16*)x, n, out);
+  else sq_norm_kernel<<<grid, kOptThreads, 0, s>>>((const float*)x, n, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_adamw(float* master, float* m, float* v, const void* grad, int grad_is_bf16, void* param_bf16,
+                         uint64_t n, const AdamWArgs& a, const float* total_sq_norm, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  const int grid = grid_for(n, kOptThreads, 8);
+  if (grad_is_bf16)
+    adamw_kernel<<<grid, kOptThreads, 0, s>>>(master, m, v, (const __nv_bfloat16*)grad, (__nv_bfloat16*)param_bf16, n, a,
+                                              total_sq_norm);
+  else
+    adamw_kernel<<<grid, kOptThreads, 0, s>>>(master, m, v, (const float*)grad, (__nv_bfloat16*)param_bf16, n, a,
+                                              total_sq_norm);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ce_fwd_bwd(void* logits_bf16, const int64_t* targets, float* loss_sum, int64_t rows, int vocab,
+                              int64_t row_stride, float grad_scale, int64_t ignore_index, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  const size_t smem = (size_t)vocab * sizeof(__nv_bfloat16);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;   // the row must fit into shared memory
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(ce_fwd_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  ce_fwd_bwd_kernel<<<(unsigned)rows, 512, smem, s>>>((__nv_bfloat16*)logits_bf16, targets, loss_sum, vocab, row_stride,
+                                                      grad_scale, ignore_index);
+  return cudaGetLastError();
+}
+
+}  // namespace pccl

@@ -1,0 +1,25 @@
+// Launchers of the elementwise training kernels (optim.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pccl {
+
+struct AdamWArgs {
+  float lr, beta1, beta2, eps, weight_decay;
+  float bias1, bias2;      // 1/(1-beta1^t), 1/(1-beta2^t)
+  float grad_scale;        // multiplies the stored gradient (e.g. loss-scale inverse)
+  float max_grad_norm;     // <= 0: no clipping
+};
+
+// *out += sum(x^2); out must be zeroed by the caller.
+cudaError_t launch_sq_norm(const void* x, int dtype_is_bf16, uint64_t n, float* out, cudaStream_t s);
+
+cudaError_t launch_adamw(float* master, float* m, float* v, const void* grad, int grad_is_bf16, void* param_bf16,
+                         uint64_t n, const AdamWArgs& a, const float* total_sq_norm, cudaStream_t s);
+
+// In place: logits (bf16, rows x vocab) become d(loss)/d(logits) * grad_scale; *loss_sum += sum of row losses.
+cudaError_t launch_ce_fwd_bwd(void* logits_bf16, const int64_t* targets, float* loss_sum, int64_t rows, int vocab,
+                              int64_t row_stride, float grad_scale, int64_t ignore_index, cudaStream_t s);
+
+}  // namespace pccl

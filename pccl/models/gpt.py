@@ -1,0 +1,256 @@
+"""GPT-2-style decoder written as explicit forward and backward functions over flat
+parameter views.
+
+The reference ships no model: its DeepSpeed hook (``pccl/patch_deepspeed.py:95-126``)
+expects an external GPT training script.  The benchmark configurations name two models
+(1.3B: 24 layers, d_model 2048, 16 heads, FFN 8192; 7B: 32 layers, d_model 4096, 32 heads,
+FFN 16384; GELU, vocabulary 50304, sequence 2048, tied embeddings, N(0, 0.02) init), and
+this module provides them in the form a ZeRO-3 engine wants: parameters grouped in
+"units" that are gathered and released one at a time, a forward that keeps only what the
+backward needs, and a backward that writes weight gradients straight into a flat
+gradient buffer (no autograd graph, no per-parameter ``.grad`` tensors to copy).
+
+GEMMs go to cuBLAS through ``torch``; the two GEMMs that directly consume a freshly
+gathered weight (QKV and FC1) can be replaced by the fused all-gather+GEMM kernel through
+the ``linear_fwd`` hook of ``LayerParams``.  The attention core uses
+``scaled_dot_product_attention`` under a local autograd scope.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+
+@dataclass(frozen=True)
+class GPTConfig:
+    n_layer: int
+    d_model: int
+    n_head: int
+    d_ff: int
+    vocab: int = 50304
+    seq_len: int = 2048
+    init_std: float = 0.02
+    ln_eps: float = 1e-5
+    name: str = "gpt"
+
+    @property
+    def head_dim(self) -> int:
+        return self.d_model // self.n_head
+
+    def num_params(self) -> int:
+        return sum(u.numel for u in unit_specs(self))
+
+    def flops_per_token(self) -> float:
+        """Forward+backward matmul FLOPs per token: 6 per dense weight, plus causal
+        attention (QK^T and PV, half of the square)."""
+        dense = self.n_layer * (4 * self.d_model * self.d_model + 2 * self.d_model * self.d_ff) + self.vocab * self.d_model
+        attn = self.n_layer * self.seq_len * self.d_model
+        return 6.0 * dense + 6.0 * attn
+
+
+PRESETS: Dict[str, GPTConfig] = {
+    "gpt-1.3b": GPTConfig(24, 2048, 16, 8192, name="gpt-1.3b"),
+    "gpt-7b": GPTConfig(32, 4096, 32, 16384, name="gpt-7b"),
+    "gpt-350m": GPTConfig(24, 1024, 16, 4096, name="gpt-350m"),
+    "gpt-tiny": GPTConfig(2, 256, 4, 1024, vocab=1024, seq_len=128, name="gpt-tiny"),
+}
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: Tuple[int, ...]
+    init: str           # "normal" | "zeros" | "ones"
+    offset: int = 0     # element offset inside the unit
+
+    @property
+    def numel(self) -> int:
+        return math.prod(self.shape)
+
+
+@dataclass
+class UnitSpec:
+    name: str
+    params: List[ParamSpec]
+    numel: int = 0      # unpadded size; parameters are laid out back to back, 256-element aligned
+
+
+_ALIGN = 256
+
+
+def _layout(name: str, params: List[ParamSpec]) -> UnitSpec:
+    off = 0
+    for p in params:
+        off = (off + _ALIGN - 1) // _ALIGN * _ALIGN
+        p.offset = off
+        off += p.numel
+    return UnitSpec(name, params, off)
+
+
+def unit_specs(cfg: GPTConfig) -> List[UnitSpec]:
+    """Unit 0 holds the embeddings and the final layer norm (the head needs both and the
+    token embedding is tied to the output projection); units 1..L are the blocks."""
+    d, f = cfg.d_model, cfg.d_ff
+    units = [_layout("embed", [
+        ParamSpec("wte", (cfg.vocab, d), "normal"),
+        ParamSpec("wpe", (cfg.seq_len, d), "normal"),
+        ParamSpec("lnf_w", (d,), "ones"),
+        ParamSpec("lnf_b", (d,), "zeros"),
+    ])]
+    for i in range(cfg.n_layer):
+        units.append(_layout(f"layer{i}", [
+            ParamSpec("qkv_w", (3 * d, d), "normal"),
+            ParamSpec("fc1_w", (f, d), "normal"),
+            ParamSpec("proj_w", (d, d), "normal"),
+            ParamSpec("fc2_w", (d, f), "normal"),
+            ParamSpec("qkv_b", (3 * d,), "zeros"),
+            ParamSpec("fc1_b", (f,), "zeros"),
+            ParamSpec("proj_b", (d,), "zeros"),
+            ParamSpec("fc2_b", (d,), "zeros"),
+            ParamSpec("ln1_w", (d,), "ones"),
+            ParamSpec("ln1_b", (d,), "zeros"),
+            ParamSpec("ln2_w", (d,), "ones"),
+            ParamSpec("ln2_b", (d,), "zeros"),
+        ]))
+    return units
+
+
+def views(unit: UnitSpec, flat: torch.Tensor) -> Dict[str, torch.Tensor]:
+    """Named parameter views into a flat buffer that holds the unit."""
+    return {p.name: flat[p.offset:p.offset + p.numel].view(p.shape) for p in unit.params}
+
+
+def init_unit(unit: UnitSpec, flat: torch.Tensor, cfg: GPTConfig, seed: int) -> None:
+    """Fill a full (gathered-size) fp32 buffer with the unit's initial values.  The values
+    depend on (seed, unit, parameter) only, never on how many ranks shard the unit."""
+    flat.zero_()
+    for idx, p in enumerate(unit.params):
+        v = flat[p.offset:p.offset + p.numel]
+        if p.init == "normal":
+            g = torch.Generator(device=flat.device).manual_seed(seed * 1000003 + idx)
+            v.normal_(0.0, cfg.init_std, generator=g)
+        elif p.init == "ones":
+            v.fill_(1.0)
+
+
+# ---------------------------------------------------------------------------- layer math
+LinearFwd = Callable[[torch.Tensor, torch.Tensor, Optional[torch.Tensor], str], torch.Tensor]
+
+
+def _default_linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], which: str) -> torch.Tensor:
+    return F.linear(x, w, b)
+
+
+def _ln_fwd(x, w, b, eps):
+    return torch.ops.aten.native_layer_norm(x, [x.shape[-1]], w, b, eps)
+
+
+def _ln_bwd(dy, x, mean, rstd, w, b, gw, gb):
+    dx, dw, db = torch.ops.aten.native_layer_norm_backward(dy, x, [x.shape[-1]], mean, rstd, w, b, [True, True, True])
+    gw.copy_(dw)
+    gb.copy_(db)
+    return dx
+
+
+def _wgrad(dy: torch.Tensor, x: torch.Tensor, gw: torch.Tensor, gb: Optional[torch.Tensor]) -> None:
+    torch.mm(dy.t(), x, out=gw)
+    if gb is not None:
+        torch.sum(dy, dim=0, out=gb)
+
+
+def layer_forward(x: torch.Tensor, p: Dict[str, torch.Tensor], cfg: GPTConfig, batch: int,
+                  linear_fwd: LinearFwd = _default_linear):
+    """x: [T, d] with T = batch * seq.  Returns (y, ctx)."""
+    T, d = x.shape
+    S, H, dh = T // batch, cfg.n_head, cfg.head_dim
+    h1, mean1, rstd1 = _ln_fwd(x, p["ln1_w"], p["ln1_b"], cfg.ln_eps)
+    qkv = linear_fwd(h1, p["qkv_w"], p["qkv_b"], "qkv")                  # [T, 3d]
+    q, k, v = (t.transpose(1, 2) for t in qkv.view(batch, S, 3, H, dh).unbind(2))   # [B, H, S, dh] views
+    qd, kd, vd = (t.detach().requires_grad_() for t in (q, k, v))
+    with torch.enable_grad():
+        att = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True)            # [B, H, S, dh]
+    a = att.detach().transpose(1, 2).reshape(T, d)
+    x2 = torch.addmm(p["proj_b"], a, p["proj_w"].t()).add_(x)
+    h2, mean2, rstd2 = _ln_fwd(x2, p["ln2_w"], p["ln2_b"], cfg.ln_eps)
+    u = linear_fwd(h2, p["fc1_w"], p["fc1_b"], "fc1")                    # [T, f]
+    g = F.gelu(u, approximate="tanh")
+    y = torch.addmm(p["fc2_b"], g, p["fc2_w"].t()).add_(x2)
+    ctx = (x, mean1, rstd1, h1, qd, kd, vd, att, a, x2, mean2, rstd2, h2, u, g)
+    return y, ctx
+
+
+def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[str, torch.Tensor], cfg: GPTConfig,
+                   batch: int) -> torch.Tensor:
+    """Returns dx; writes every parameter gradient of the layer into the views ``gr``."""
+    x, mean1, rstd1, h1, qd, kd, vd, att, a, x2, mean2, rstd2, h2, u, g = ctx
+    T, d = x.shape
+    S, H, dh = T // batch, cfg.n_head, cfg.head_dim
+    _wgrad(dy, g, gr["fc2_w"], gr["fc2_b"])
+    dg = torch.mm(dy, p["fc2_w"])
+    du = torch.ops.aten.gelu_backward(dg, u, approximate="tanh")
+    del dg
+    _wgrad(du, h2, gr["fc1_w"], gr["fc1_b"])
+    dh2 = torch.mm(du, p["fc1_w"])
+    del du
+    dx2 = _ln_bwd(dh2, x2, mean2, rstd2, p["ln2_w"], p["ln2_b"], gr["ln2_w"], gr["ln2_b"]).add_(dy)
+    _wgrad(dx2, a, gr["proj_w"], gr["proj_b"])
+    da = torch.mm(dx2, p["proj_w"])
+    datt = da.view(batch, S, H, dh).transpose(1, 2)
+    dq, dk, dv = torch.autograd.grad(att, (qd, kd, vd), datt)
+    dqkv = torch.empty(batch, S, 3, H, dh, dtype=x.dtype, device=x.device)
+    dqkv[:, :, 0].copy_(dq.transpose(1, 2))
+    dqkv[:, :, 1].copy_(dk.transpose(1, 2))
+    dqkv[:, :, 2].copy_(dv.transpose(1, 2))
+    dqkv = dqkv.view(T, 3 * d)
+    _wgrad(dqkv, h1, gr["qkv_w"], gr["qkv_b"])
+    dh1 = torch.mm(dqkv, p["qkv_w"])
+    dx = _ln_bwd(dh1, x, mean1, rstd1, p["ln1_w"], p["ln1_b"], gr["ln1_w"], gr["ln1_b"]).add_(dx2)
+    return dx
+
+
+def embed_forward(tokens: torch.Tensor, p: Dict[str, torch.Tensor]) -> torch.Tensor:
+    """tokens: [B, S] int64 -> [B*S, d]."""
+    B, S = tokens.shape
+    x = F.embedding(tokens, p["wte"])
+    x = x + p["wpe"][:S].unsqueeze(0)
+    return x.view(B * S, -1)
+
+
+def embed_backward(dx: torch.Tensor, tokens: torch.Tensor, gr: Dict[str, torch.Tensor]) -> None:
+    """Accumulates into gr["wte"] (the head already wrote its share) and writes gr["wpe"]."""
+    B, S = tokens.shape
+    gr["wte"].index_add_(0, tokens.reshape(-1), dx)
+    gw = gr["wpe"]
+    gw.zero_()
+    gw[:S].copy_(dx.view(B, S, -1).sum(0))
+
+
+def head_forward_backward(x: torch.Tensor, targets: torch.Tensor, p: Dict[str, torch.Tensor],
+                          gr: Dict[str, torch.Tensor], cfg: GPTConfig, grad_scale: float, loss_sum: torch.Tensor,
+                          ce_fwd_bwd: Callable, chunk_tokens: int = 4096) -> torch.Tensor:
+    """Final layer norm, tied output projection and cross-entropy, forward and backward in
+    one sweep over token chunks so the [T, vocab] logits never exist in full.  Adds the
+    summed token losses to ``loss_sum``; writes gr["wte"], gr["lnf_*"]; returns dx."""
+    T, d = x.shape
+    hf, mean, rstd = _ln_fwd(x, p["lnf_w"], p["lnf_b"], cfg.ln_eps)
+    wte = p["wte"]
+    dhf = torch.empty_like(hf)
+    gw = gr["wte"]
+    tflat = targets.reshape(-1)
+    first = True
+    for s in range(0, T, chunk_tokens):
+        e = min(T, s + chunk_tokens)
+        logits = torch.mm(hf[s:e], wte.t())                     # [c, V] bf16
+        ce_fwd_bwd(logits, tflat[s:e], loss_sum, grad_scale)    # logits -> dlogits, in place
+        torch.mm(logits, wte, out=dhf[s:e])
+        if first:
+            torch.mm(logits.t(), hf[s:e], out=gw)
+            first = False
+        else:
+            gw.addmm_(logits.t(), hf[s:e])
+        del logits
+    return _ln_bwd(dhf, x, mean, rstd, p["lnf_w"], p["lnf_b"], gr["lnf_w"], gr["lnf_b"])

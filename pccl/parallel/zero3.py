@@ -1,0 +1,247 @@
+"""A ZeRO-3 (fully sharded data parallel) training engine for the GPT models.
+
+The reference re-routes DeepSpeed's ZeRO-3 collectives (``pccl/patch_deepspeed.py:29-59``)
+but contains no engine; DeepSpeed is not a dependency here, so this is the engine that
+the hooks serve.  It talks to a backend object with DeepSpeed's five method names
+(``pccl.parallel.backend.TorchBackend``): unpatched, that is ``torch.distributed`` over
+NCCL (the baseline arm); after ``pccl.patch_deepspeed.patch_deepspeed`` the very same
+engine gathers parameters and reduces gradients through this library's kernels.
+
+Memory plan (per rank, P ranks, N parameters):
+  bf16 parameter shard N/P, fp32 master + Adam moments 12 N/P, gradient shard 2-4 N/P,
+  two rotating gathered-parameter buffers and two rotating gradient buffers of the
+  largest unit (bf16), one dedicated gradient buffer for the embedding unit.
+With the patched backend all communication buffers live in the symmetric heap, so
+all-gathers write straight into the peers' buffers and nothing is staged.
+
+Step schedule: the parameters are cut into units (embedding+final norm, then one unit per
+transformer block).  Forward walks the units, prefetching unit k+1 on the communication
+stream while unit k computes; the head re-gathers the embedding; backward walks the
+blocks in reverse, re-gathering each unit, and hands every unit's gradient buffer to an
+asynchronous reduce-scatter as soon as its backward is done.  The optimizer is one fused
+AdamW kernel over the whole shard, with global-norm clipping computed on the device.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models import gpt
+from ..models.gpt import GPTConfig
+from .backend import TorchBackend
+
+
+def _wait(handle) -> None:
+    if handle is not None:
+        handle.wait()
+
+
+@dataclass
+class OptimConfig:
+    lr: float = 1e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+    max_grad_norm: float = 1.0
+
+
+def heap_bytes_needed(cfg: GPTConfig, world: int) -> int:
+    """Symmetric-heap bytes the engine allocates for ``cfg`` on ``world`` ranks (without
+    the communicator's staging area)."""
+    units = gpt.unit_specs(cfg)
+    gran = world * 256
+    padded = [(u.numel + gran - 1) // gran * gran for u in units]
+    total_shard = sum(n // world for n in padded)
+    max_layer = max(padded[1:]) if len(padded) > 1 else padded[0]
+    elems = total_shard + 2 * max(padded) + 2 * max_layer + padded[0]
+    return 2 * elems + (64 << 20)
+
+
+class Zero3Engine:
+    def __init__(self, cfg: GPTConfig, backend: Optional[TorchBackend] = None, optim: Optional[OptimConfig] = None,
+                 device: Optional[torch.device] = None, seed: int = 1234, comm=None, group=None,
+                 linear_fwd: Optional[Callable] = None, micro_batch: int = 1):
+        from .. import build_kernels
+
+        self.C = build_kernels.load()
+        self.cfg = cfg
+        self.backend = backend or TorchBackend()
+        self.optim = optim or OptimConfig()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.comm = comm
+        self.linear_fwd = linear_fwd or gpt._default_linear
+        self.micro_batch = micro_batch
+        self.step_count = 0
+        self.launches = 0          # kernels of this library launched by the last step
+        self.units = gpt.unit_specs(cfg)
+        P = self.world
+        gran = P * 256
+        self.padded = [(u.numel + gran - 1) // gran * gran for u in self.units]
+        self.shard_len = [n // P for n in self.padded]
+        self.shard_off = [0]
+        for n in self.shard_len:
+            self.shard_off.append(self.shard_off[-1] + n)
+        total_shard = self.shard_off[-1]
+        max_unit = max(self.padded)
+        max_layer = max(self.padded[1:]) if len(self.padded) > 1 else self.padded[0]
+        sym = bool(getattr(self.backend, "symmetric_memory", False)) and comm is not None and comm.native is not None
+        self.symmetric = sym
+
+        def alloc(n: int) -> torch.Tensor:
+            if sym:
+                return comm.empty(n, torch.bfloat16)
+            return torch.empty(n, dtype=torch.bfloat16, device=self.device)
+
+        self.param_shard = alloc(total_shard)
+        self.gathered = [alloc(max_unit), alloc(max_unit)]
+        self.gradbuf = [alloc(max_layer), alloc(max_layer)]
+        self.gradbuf0 = alloc(self.padded[0])
+        for b in self.gradbuf + [self.gradbuf0]:
+            b.zero_()
+        self.fused_scale = bool(getattr(self.backend, "fused_scale", False))
+        gdt = torch.float32 if self.fused_scale else torch.bfloat16
+        self.grad_shard = torch.zeros(total_shard, dtype=gdt, device=self.device)
+        self.master = torch.empty(total_shard, dtype=torch.float32, device=self.device)
+        self.exp_avg = torch.zeros(total_shard, dtype=torch.float32, device=self.device)
+        self.exp_avg_sq = torch.zeros(total_shard, dtype=torch.float32, device=self.device)
+        self.sq_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.loss_sum = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._init_params(seed)
+        # views of every unit in each rotating buffer
+        self.pviews = [[gpt.views(u, buf) for buf in self.gathered] for u in self.units]
+        self.gviews = [None] + [[gpt.views(u, buf) for buf in self.gradbuf] for u in self.units[1:]]
+        self.gviews0 = gpt.views(self.units[0], self.gradbuf0)
+        self.main = torch.cuda.current_stream(self.device)
+        self._rs_pending: List = [None, None]
+        self._tokens_dev: Optional[torch.Tensor] = None
+        self._targets_dev: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ setup
+    def _init_params(self, seed: int) -> None:
+        P, r = self.world, self.rank
+        for ui, u in enumerate(self.units):
+            full = torch.empty(self.padded[ui], dtype=torch.float32, device=self.device)
+            gpt.init_unit(u, full, self.cfg, seed + ui)
+            mine = full.view(P, -1)[r]
+            sl = slice(self.shard_off[ui], self.shard_off[ui + 1])
+            self.master[sl].copy_(mine)
+            self.param_shard[sl].copy_(mine)
+            del full
+        torch.cuda.synchronize(self.device)
+
+    # ------------------------------------------------------------------ communication
+    def _gather(self, ui: int, slot: int):
+        """Start the all-gather of unit ``ui`` into rotating buffer ``slot``."""
+        out = self.gathered[slot][: self.padded[ui]]
+        inp = self.param_shard[self.shard_off[ui]: self.shard_off[ui + 1]]
+        return self.backend.all_gather_into_tensor(out, inp, group=self.group, async_op=True)
+
+    def _reduce(self, ui: int, buf: torch.Tensor):
+        """Start the reduce-scatter of unit ``ui``'s gradient buffer into the gradient shard."""
+        inp = buf[: self.padded[ui]]
+        out = self.grad_shard[self.shard_off[ui]: self.shard_off[ui + 1]]
+        if self.fused_scale:
+            return self.backend.reduce_scatter_tensor(out, inp, group=self.group, async_op=True, scale=1.0 / self.world)
+        return self.backend.reduce_scatter_tensor(out, inp, group=self.group, async_op=True)
+
+    # ------------------------------------------------------------------ one training step
+    @torch.no_grad()
+    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """tokens, targets: [B, S] int64, on the host (pinned) or on the device.  Runs
+        forward, backward, gradient reduction and the optimizer; returns the mean loss of
+        this rank's micro-batch as a one-element device tensor."""
+        cfg, C = self.cfg, self.C
+        if tokens.device.type != "cuda":
+            if self._tokens_dev is None or self._tokens_dev.shape != tokens.shape:
+                self._tokens_dev = torch.empty(tokens.shape, dtype=torch.int64, device=self.device)
+                self._targets_dev = torch.empty(targets.shape, dtype=torch.int64, device=self.device)
+            self._tokens_dev.copy_(tokens, non_blocking=True)
+            self._targets_dev.copy_(targets, non_blocking=True)
+            tokens, targets = self._tokens_dev, self._targets_dev
+        B, S = tokens.shape
+        T = B * S
+        L = cfg.n_layer
+        launches0 = self._native_launches()
+        self.loss_sum.zero_()
+        self.sq_norm.zero_()
+        # without a fused scale in the reduce-scatter the 1/P of the average rides on the loss gradient
+        grad_scale = 1.0 / T if self.fused_scale else 1.0 / (T * self.world)
+
+        # ---- forward
+        stage = 0
+        pending = self._gather(0, 0)
+        nxt = self._gather(1, 1) if L > 0 else None
+        _wait(pending)
+        x = gpt.embed_forward(tokens, self.pviews[0][0])
+        saved = []
+        for li in range(1, L + 1):
+            slot = li % 2
+            _wait(nxt)
+            # the buffer that the next prefetch overwrites was last read by the previous stage,
+            # which is already queued on this stream; the async launch orders itself after it
+            nxt = self._gather(li + 1, 1 - slot) if li < L else self._gather(0, 1 - slot)
+            x, ctx = gpt.layer_forward(x, self.pviews[li][slot], cfg, B, self.linear_fwd)
+            saved.append(ctx)
+        # ---- head: final norm, tied projection, loss; forward and backward together
+        head_slot = (L + 1) % 2
+        _wait(nxt)
+        nxt = self._gather(L, 1 - head_slot) if L > 0 else None
+        dx = gpt.head_forward_backward(x, targets, self.pviews[0][head_slot], self.gviews0, cfg, grad_scale,
+                                       self.loss_sum, self._ce)
+        # ---- backward through the blocks
+        for li in range(L, 0, -1):
+            slot = li % 2
+            _wait(nxt)
+            nxt = self._gather(li - 1, 1 - slot) if li > 1 else None
+            gslot = li % 2
+            _wait(self._rs_pending[gslot])          # the buffer's previous reduce-scatter has read it
+            dx = gpt.layer_backward(dx, saved.pop(), self.pviews[li][slot], self.gviews[li][gslot], cfg, B)
+            self._rs_pending[gslot] = self._reduce(li, self.gradbuf[gslot])
+        gpt.embed_backward(dx, tokens, self.gviews0)
+        rs0 = self._reduce(0, self.gradbuf0)
+        for h in self._rs_pending + [rs0]:
+            _wait(h)
+        self._rs_pending = [None, None]
+
+        # ---- optimizer: global-norm clipping on the device, then one fused AdamW launch
+        self.step_count += 1
+        o = self.optim
+        if o.max_grad_norm > 0:
+            C.sq_norm(self.grad_shard, self.sq_norm)
+            if self.world > 1:
+                _wait(self.backend.all_reduce(self.sq_norm, group=self.group, async_op=False))
+        C.adamw(self.master, self.exp_avg, self.exp_avg_sq, self.grad_shard, self.param_shard, o.lr, o.beta1, o.beta2,
+                o.eps, o.weight_decay, self.step_count, 1.0, o.max_grad_norm,
+                self.sq_norm if o.max_grad_norm > 0 else None)
+        own = 2 + (1 if o.max_grad_norm > 0 else 0) + (T + 4095) // 4096
+        self.launches = own + (self._native_launches() - launches0)
+        return self.loss_sum / T
+
+    def _ce(self, logits, targets, loss_sum, grad_scale) -> None:
+        self.C.ce_fwd_bwd(logits, targets, loss_sum, grad_scale, -100)
+
+    def _native_launches(self) -> int:
+        if self.comm is not None and self.comm.native is not None:
+            return int(self.comm.native.kernels_launched)
+        return 0
+
+    # ------------------------------------------------------------------ checkpoint (sharded)
+    def state_dict(self) -> Dict[str, torch.Tensor]:
+        return {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
+                "step": torch.tensor(self.step_count), "world": torch.tensor(self.world)}
+
+    def load_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
+        if int(sd["world"]) != self.world:
+            raise ValueError("sharded checkpoint was written with a different world size")
+        self.master.copy_(sd["master"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.param_shard.copy_(self.master)
+        self.step_count = int(sd["step"])

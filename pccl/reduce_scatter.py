@@ -150,13 +150,26 @@ def _reduce_scatter_2d_native(out, inp, inner: Group, outer: Group, intra: int, 
     mid = torch.empty(inter * n, dtype=inp.dtype, device=inp.device)
 
     def launch():
-        # inner level: the block for member i' is the `inter` sub-blocks (o', i'), o' = 0..inter-1
-        native.reduce_scatter_raw(inner.gid, sch.ALGO_IDS[a1], l1, tin, tin, tin, [inp.data_ptr()], [mid.data_ptr()],
-                                  0, native.staging_off, n * es, intra * n * es, n, n * es, inter, 1.0)
-        # outer level: plain reduce-scatter of the intermediate over the column
-        native.reduce_scatter_raw(outer.gid, sch.ALGO_IDS[a2], l2, tin, tin, tout, [mid.data_ptr()], [out.data_ptr()],
-                                  0, native.staging_off, n * es, 0, n, n * out.element_size(), 1, scale)
+        rs2d_inner_call(native, inner.gid, sch.ALGO_IDS[a1], l1, tin, [inp.data_ptr()], [mid.data_ptr()], n, es,
+                        intra, inter)
+        rs2d_outer_call(native, outer.gid, sch.ALGO_IDS[a2], l2, tin, tout, [mid.data_ptr()], [out.data_ptr()], n, es,
+                        out.element_size(), scale)
         if async_op:
             mid.record_stream(torch.cuda.current_stream())
 
     return run_native(inner, async_op, launch)
+
+
+def rs2d_inner_call(native, gid: int, algo_id: int, lanes: int, tin: int, in_ptrs, mid_ptrs, n: int, es: int,
+                    intra: int, inter: int) -> None:
+    """Inner level of the 2-D reduce-scatter: the block for member i' is the ``inter``
+    sub-blocks (o', i'), o' = 0..inter-1, of the global-rank-ordered input."""
+    native.reduce_scatter_raw(gid, algo_id, lanes, tin, tin, tin, list(in_ptrs), list(mid_ptrs), 0, native.staging_off,
+                              n * es, intra * n * es, n, n * es, inter, 1.0)
+
+
+def rs2d_outer_call(native, gid: int, algo_id: int, lanes: int, tin: int, tout: int, mid_ptrs, out_ptrs, n: int,
+                    es: int, out_es: int, scale: float) -> None:
+    """Outer level: plain reduce-scatter of the intermediate over the column."""
+    native.reduce_scatter_raw(gid, algo_id, lanes, tin, tin, tout, list(mid_ptrs), list(out_ptrs), 0,
+                              native.staging_off, n * es, 0, n, n * out_es, 1, scale)

@@ -1,0 +1,297 @@
+"""Collective kernels on ONE GPU: all P ranks are emulated by a single cooperative launch
+(blockIdx.y = rank) over P separate heaps, so the full flag protocol, every schedule and
+every dtype path runs exactly as it does across GPUs.  References are plain PyTorch fp32."""
+import pytest
+import torch
+
+import pccl
+from pccl import schedule as sch
+from pccl.all_gather import ag2d_inner_call, ag2d_outer_call
+from pccl.reduce_scatter import rs2d_inner_call, rs2d_outer_call
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+_comms = {}
+
+
+def emu(P):
+    if P not in _comms:
+        _comms[P] = pccl.Communicator.emulated_world(P, device=0, heap_bytes=96 << 20, staging_bytes=24 << 20)
+    return _comms[P]
+
+
+def rand(n, dtype, seed):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return torch.randn(n, generator=g, device=DEV, dtype=torch.float32).to(dtype)
+
+
+SIZES = [1, 3, 17, 4096, (1 << 18) + 5]
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+@pytest.mark.parametrize("algo", [sch.DIRECT, sch.RING, sch.RECURSIVE, sch.PULL])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_all_gather_private_buffers(P, algo, dtype):
+    comm = emu(P)
+    for n in SIZES:
+        ins = [rand(n, dtype, 10 * r + n) for r in range(P)]
+        outs = [torch.zeros(P * n, dtype=dtype, device=DEV) for _ in range(P)]
+        comm.native.all_gather(comm.world_group.gid, outs, ins, sch.ALGO_IDS[algo], 5)
+        comm.check()
+        want = torch.cat(ins)
+        for r in range(P):
+            assert torch.equal(outs[r], want), f"P={P} {algo} n={n} rank {r}"
+
+
+@pytest.mark.parametrize("P", [2, 8])
+@pytest.mark.parametrize("algo", [sch.DIRECT, sch.RING, sch.RECURSIVE, sch.PULL])
+def test_all_gather_symmetric_zero_copy(P, algo):
+    comm = emu(P)
+    n = 70001
+    outs = comm.empty(P * n, torch.bfloat16)
+    sym_in = comm.empty(n, torch.bfloat16)
+    vals = [rand(n, torch.bfloat16, 3 + r) for r in range(P)]
+    for r in range(P):
+        outs[r].zero_()
+        sym_in[r].copy_(vals[r])
+    comm.native.all_gather(comm.world_group.gid, outs, sym_in, sch.ALGO_IDS[algo], 7)
+    comm.check()
+    want = torch.cat(vals)
+    for r in range(P):
+        assert torch.equal(outs[r], want)
+    # in place: the contribution already sits in its slot of the output
+    for r in range(P):
+        outs[r].zero_()
+        outs[r][r * n:(r + 1) * n].copy_(vals[r])
+    if algo != sch.PULL:
+        comm.native.all_gather(comm.world_group.gid, outs, [outs[r][r * n:(r + 1) * n] for r in range(P)],
+                               sch.ALGO_IDS[algo], 3)
+        comm.check()
+        for r in range(P):
+            assert torch.equal(outs[r], want)
+    del outs, sym_in
+
+
+def rs_reference(ins, P, n, scale, out_dtype):
+    total = sum(t.float() for t in ins).view(P, n) * scale
+    return [total[r].to(out_dtype) for r in range(P)]
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+@pytest.mark.parametrize("algo", [sch.DIRECT, sch.RING, sch.RECURSIVE])
+@pytest.mark.parametrize("dtypes", [(torch.bfloat16, None, torch.bfloat16), (torch.bfloat16, torch.float32, torch.float32),
+                                    (torch.float32, None, torch.float32), (torch.float16, None, torch.float32)])
+def test_reduce_scatter_push(P, algo, dtypes):
+    tin, wire, tout = dtypes
+    comm = emu(P)
+    for n in SIZES:
+        ins = [rand(P * n, tin, 100 * r + n) for r in range(P)]
+        outs = [torch.zeros(n, dtype=tout, device=DEV) for _ in range(P)]
+        scale = 1.0 / P
+        comm.native.reduce_scatter(comm.world_group.gid, outs, ins, sch.ALGO_IDS[algo], 4, scale, wire)
+        comm.check()
+        want = rs_reference(ins, P, n, scale, tout)
+        exact_partials = wire == torch.float32 or tin == torch.float32 or algo == sch.DIRECT
+        for r in range(P):
+            if exact_partials:
+                # single rounding: only fp32 reassociation separates us from the reference
+                tol = dict(rtol=1e-5, atol=1e-5) if tout == torch.float32 else dict(rtol=8e-3, atol=1e-5)
+            else:
+                tol = dict(rtol=3e-2, atol=3e-2)       # partial sums were rounded to 16 bits on the wire
+            torch.testing.assert_close(outs[r].float(), want[r].float(), **tol)
+
+
+@pytest.mark.parametrize("P", [2, 8])
+def test_reduce_scatter_pull_symmetric_input(P):
+    comm = emu(P)
+    n = 40003
+    sym = comm.empty(P * n, torch.bfloat16)
+    vals = [rand(P * n, torch.bfloat16, 50 + r) for r in range(P)]
+    for r in range(P):
+        sym[r].copy_(vals[r])
+    outs = [torch.zeros(n, dtype=torch.float32, device=DEV) for _ in range(P)]
+    comm.native.reduce_scatter(comm.world_group.gid, outs, sym, sch.ALGO_IDS[sch.PULL], 6, 0.5, None)
+    comm.check()
+    want = rs_reference(vals, P, n, 0.5, torch.float32)
+    for r in range(P):
+        torch.testing.assert_close(outs[r], want[r], rtol=1e-5, atol=1e-5)
+    priv = [v.clone() for v in vals]
+    with pytest.raises(RuntimeError):
+        comm.native.reduce_scatter(comm.world_group.gid, outs, priv, sch.ALGO_IDS[sch.PULL], 6, 1.0, None)
+    del sym
+
+
+def test_reduce_scatter_bf16_accumulates_in_fp32():
+    """Many equal small addends: a 16-bit accumulator would stall, fp32 does not."""
+    P = 8
+    comm = emu(P)
+    n = 1024
+    ins = []
+    for r in range(P):
+        t = torch.full((P * n,), 1.0 if r == 0 else 2.0 ** -9, dtype=torch.bfloat16, device=DEV)
+        ins.append(t)
+    outs = [torch.zeros(n, dtype=torch.float32, device=DEV) for _ in range(P)]
+    comm.native.reduce_scatter(comm.world_group.gid, outs, ins, sch.ALGO_IDS[sch.DIRECT], 2, 1.0, None)
+    comm.check()
+    assert torch.all(outs[3] == 1.0 + 7 * 2.0 ** -9)
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_all_reduce(P, dtype):
+    comm = emu(P)
+    for n in [1, 9, 1000, (1 << 17) + 3]:
+        ts = [rand(n, dtype, 7 * r + n) for r in range(P)]
+        want = sum(t.float() for t in ts)
+        comm.native.all_reduce(comm.world_group.gid, ts, sch.ALGO_IDS[sch.DIRECT], 4, 1.0)
+        comm.check()
+        for r in range(P):
+            tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=8e-3, atol=1e-3)
+            torch.testing.assert_close(ts[r].float(), want, **tol)
+            assert torch.equal(ts[r], ts[0]), "all ranks must hold bit-identical results"
+    sym = comm.empty(5000, dtype)
+    vals = [rand(5000, dtype, 99 + r) for r in range(P)]
+    for r in range(P):
+        sym[r].copy_(vals[r])
+    comm.native.all_reduce(comm.world_group.gid, sym, sch.ALGO_IDS[sch.DIRECT], 3, 1.0 / P)
+    comm.check()
+    want = sum(v.float() for v in vals) / P
+    for r in range(P):
+        torch.testing.assert_close(sym[r].float(), want, rtol=8e-3, atol=1e-3)
+    del sym
+
+
+@pytest.mark.parametrize("P", [2, 8])
+def test_broadcast_and_barrier(P):
+    comm = emu(P)
+    for root in (0, P - 1):
+        for n in (5, 100003):
+            ts = [torch.full((n,), float(r), device=DEV) for r in range(P)]
+            comm.native.broadcast(comm.world_group.gid, ts, root, 4, False)
+            comm.check()
+            for r in range(P):
+                assert torch.all(ts[r] == float(root))
+    for _ in range(3):
+        comm.native.barrier(comm.world_group.gid)
+    comm.check()
+
+
+def test_subgroups_and_2d_hierarchy():
+    """Inner/outer groups of a 2x2 grid, driven group by group, give the flat result
+    without any permute pass."""
+    comm = emu(4)
+    pgs = pccl.ProcessGroups(2, 2, comm=comm)
+    intra = inter = 2
+    n = 3001
+    native = comm.native
+    vals = [rand(n, torch.bfloat16, 11 + r) for r in range(4)]
+    outs = [torch.zeros(4 * n, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    nb = n * 2
+    recv_off = native.staging_off
+    for col, g in enumerate(pgs.all_outer_groups):          # ranks {col, col+2}
+        ag2d_outer_call(native, g.gid, sch.ALGO_IDS[sch.RECURSIVE], 3, [vals[r].data_ptr() for r in g.ranks], recv_off,
+                        col, nb, intra)
+    for g in pgs.all_inner_groups:
+        ag2d_inner_call(native, g.gid, sch.ALGO_IDS[sch.RING], 3, [outs[r].data_ptr() for r in g.ranks], recv_off, nb,
+                        intra, inter)
+    comm.check()
+    want = torch.cat(vals)
+    for r in range(4):
+        assert torch.equal(outs[r], want)
+
+    ins = [rand(4 * n, torch.float32, 21 + r) for r in range(4)]
+    mids = [torch.zeros(inter * n, device=DEV) for _ in range(4)]
+    res = [torch.zeros(n, device=DEV) for _ in range(4)]
+    for g in pgs.all_inner_groups:
+        rs2d_inner_call(native, g.gid, sch.ALGO_IDS[sch.RECURSIVE], 3, 2, [ins[r].data_ptr() for r in g.ranks],
+                        [mids[r].data_ptr() for r in g.ranks], n, 4, intra, inter)
+    for g in pgs.all_outer_groups:
+        rs2d_outer_call(native, g.gid, sch.ALGO_IDS[sch.RING], 3, 2, 2, [mids[r].data_ptr() for r in g.ranks],
+                        [res[r].data_ptr() for r in g.ranks], n, 4, 4, 0.25)
+    comm.check()
+    want = rs_reference(ins, 4, n, 0.25, torch.float32)
+    for r in range(4):
+        torch.testing.assert_close(res[r], want[r], rtol=1e-5, atol=1e-5)
+
+
+def test_chunking_when_staging_is_small():
+    comm = pccl.Communicator.emulated_world(4, device=0, heap_bytes=8 << 20, staging_bytes=1 << 20)
+    n = 400000                                            # 4 * 1.6 MB > 1 MiB of staging
+    ins = [rand(n, torch.float32, r) for r in range(4)]
+    outs = [torch.zeros(4 * n, device=DEV) for _ in range(4)]
+    comm.native.all_gather(comm.world_group.gid, outs, ins, sch.ALGO_IDS[sch.RING], 4)
+    big = [rand(4 * n, torch.float32, 9 + r) for r in range(4)]
+    red = [torch.zeros(n, device=DEV) for _ in range(4)]
+    comm.native.reduce_scatter(comm.world_group.gid, red, big, sch.ALGO_IDS[sch.DIRECT], 4, 1.0, None)
+    ar = [rand(3 * n, torch.float32, 30 + r) for r in range(4)]
+    want_ar = sum(ar)
+    comm.native.all_reduce(comm.world_group.gid, ar, sch.ALGO_IDS[sch.DIRECT], 4, 1.0)
+    comm.check()
+    for r in range(4):
+        assert torch.equal(outs[r], torch.cat(ins))
+        torch.testing.assert_close(red[r], rs_reference(big, 4, n, 1.0, torch.float32)[r], rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(ar[r], want_ar, rtol=1e-5, atol=1e-5)
+
+
+def test_argument_checks():
+    comm = emu(2)
+    gid = comm.world_group.gid
+    a = [torch.zeros(10, device=DEV) for _ in range(2)]
+    with pytest.raises(RuntimeError):       # wrong output size
+        comm.native.all_gather(gid, a, a, 0, 1)
+    with pytest.raises(RuntimeError):       # not divisible by world size
+        comm.native.reduce_scatter(gid, [torch.zeros(5, device=DEV)] * 2, [torch.zeros(11, device=DEV)] * 2, 0, 1, 1.0, None)
+    with pytest.raises(RuntimeError):       # non-contiguous
+        nc = [torch.zeros(20, device=DEV)[::2] for _ in range(2)]
+        comm.native.all_gather(gid, [torch.zeros(20, device=DEV)] * 2, nc, 0, 1)
+    with pytest.raises(RuntimeError):       # integer dtype cannot be reduced
+        comm.native.all_reduce(gid, [torch.zeros(4, dtype=torch.int32, device=DEV)] * 2, 0, 1, 1.0)
+    c3 = pccl.Communicator.emulated_world(3, device=0, heap_bytes=4 << 20, staging_bytes=1 << 20)
+    t = [torch.zeros(3, device=DEV) for _ in range(3)]
+    o = [torch.zeros(9, device=DEV) for _ in range(3)]
+    with pytest.raises(RuntimeError):       # recursive doubling needs a power of two
+        c3.native.all_gather(c3.world_group.gid, o, t, sch.ALGO_IDS[sch.RECURSIVE], 1)
+    c3.native.all_gather(c3.world_group.gid, o, t, sch.ALGO_IDS[sch.RING], 1)   # ring takes any size
+    c3.check()
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    """A rank whose peers never show up: the kernel gives up after its budget, says where,
+    and returns.  Nothing traps; the device stays usable; recover() clears the failure."""
+    comm = pccl.Communicator.with_fake_peers(2, rank=0, device=0, timeout_ms=50.0)
+    x = torch.ones(1000, device=DEV)
+    out = torch.zeros(2000, device=DEV)
+    pccl._all_gather(out, x, comm.world_group, use_pccl_cpp_backend=True, algorithm=sch.DIRECT)
+    with pytest.raises(pccl.PcclTimeoutError) as err:
+        comm.check()
+    assert "entry" in str(err.value) and "rank 1" in str(err.value)
+    # the context is healthy: ordinary work still runs
+    assert float((torch.ones(10, device=DEV) * 2).sum()) == 20.0
+    comm.recover()
+    comm.check()
+    # after a failure and recovery the same thing happens again, cleanly
+    comm.native.barrier(comm.world_group.gid)
+    with pytest.raises(pccl.PcclTimeoutError):
+        comm.check()
+    comm.recover()
+
+
+def test_python_api_on_single_rank_world():
+    """world == 1: every collective degenerates to a local copy / scale through the kernels."""
+    comm = pccl.Communicator.emulated_world(1, device=0, heap_bytes=4 << 20, staging_bytes=1 << 20)
+    g = comm.world_group
+    x = rand(1001, torch.bfloat16, 1)
+    out = torch.zeros_like(x)
+    pccl._all_gather(out, x, g, use_pccl_cpp_backend=True)
+    assert torch.equal(out, x)
+    o32 = torch.zeros(1001, device=DEV)
+    pccl._reduce_scatter(o32, x, g, use_pccl_cpp_backend=True, scale=0.5)
+    torch.testing.assert_close(o32, x.float() * 0.5)
+    y = x.clone()
+    pccl._all_reduce(y, g, algorithm="auto", scale=2.0)
+    torch.testing.assert_close(y.float(), x.float() * 2.0, rtol=8e-3, atol=1e-3)
+    req = pccl._all_gather(out, x, g, async_op=True, use_pccl_cpp_backend=True)
+    req.wait()
+    pccl.barrier(g)
+    comm.check()
