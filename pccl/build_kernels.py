@@ -41,6 +41,7 @@ SOURCES = [
     "collectives.cu",
     "gemm_sm100.cu",
     "optim.cu",
+    "noalloc.cu",
 ]
 
 NVCC_FLAGS = [
