@@ -18,6 +18,7 @@ Bootstrap transports, tried in this order unless ``PCCL_BOOTSTRAP`` names one:
 """
 from __future__ import annotations
 
+import array
 import atexit
 import os
 import socket
@@ -152,6 +153,7 @@ class Communicator:
         for name in order:
             try:
                 tables = getattr(self, f"_bootstrap_{name}")(C, heap_bytes, sig_bytes, enable_nvls)
+                self._self_check(C, tables[1], sig_bytes)
                 ok, msg = True, ""
             except Exception as exc:  # noqa: BLE001 - every failure means "try the next transport"
                 ok, msg = False, f"{type(exc).__name__}: {exc}"
@@ -293,8 +295,8 @@ class Communicator:
                     src, tag, fds = chan.recv()
                     if tag != 0 or len(fds) != 2:
                         raise PcclError("unexpected message while exchanging memory handles")
-                    ph = C.VmmSegment(self.device, fds[0], heap.bytes)
-                    ps = C.VmmSegment(self.device, fds[1], sig.bytes)
+                    ph = C.VmmSegment.from_fd(self.device, fds[0], heap.bytes)
+                    ps = C.VmmSegment.from_fd(self.device, fds[1], sig.bytes)
                     self._segments += [ph, ps]
                     heaps[src], sigs[src] = ph.ptr, ps.ptr
 
@@ -331,6 +333,7 @@ class Communicator:
         hdl = symm_mem.rendezvous(buf, group.group_name)
         buf.zero_()
         torch.cuda.synchronize(self.device)
+        self._agree(lambda: None)        # nobody writes into a peer before that peer has cleared its memory
         self._keepalive += [buf, hdl]
         ptrs = list(hdl.buffer_ptrs)
         sigs = [int(p) for p in ptrs]
@@ -339,6 +342,32 @@ class Communicator:
         if enable_nvls and getattr(hdl, "multicast_ptr", 0):
             mc = int(hdl.multicast_ptr) + sig_bytes
         return heaps, sigs, mc, heap_bytes
+
+    def _self_check(self, C, sigs: List[int], sig_bytes: int) -> None:
+        """Prove that every mapping reaches the peer's memory: each rank writes a word into the
+        tail of every peer's signal pad, then reads its own pad back.  A transport that maps
+        but does not deliver fails here, on all ranks together, and the next one is tried."""
+        if self.world == 1:
+            return
+        words = sig_bytes // 4
+        magic = 0x50C0FFEE
+
+        def write():
+            for p in range(self.world):
+                if p != self.rank:
+                    C.poke_u32(sigs[p] + 4 * (words - self.world + self.rank), magic + self.rank)
+
+        self._agree(write)
+
+        def read():
+            for p in range(self.world):
+                if p != self.rank:
+                    got = C.peek_u32(sigs[self.rank] + 4 * (words - self.world + p))
+                    if got != magic + p:
+                        raise PcclError(f"word written by rank {p} did not arrive (read 0x{got:x})")
+                    C.poke_u32(sigs[self.rank] + 4 * (words - self.world + p), 0)
+
+        self._agree(read)
 
     def _release_segments(self) -> None:
         for s in reversed(self._segments):
@@ -466,7 +495,9 @@ class _FdChannel:
 
     def send(self, dst: int, fds: List[int], tag: int) -> None:
         try:
-            socket.send_fds(self.sock, [struct.pack("ii", self.rank, tag)], fds, 0, self._addr(dst))
+            # socket.send_fds drops its address argument, so spell the ancillary message out
+            anc = [(socket.SOL_SOCKET, socket.SCM_RIGHTS, array.array("i", fds))]
+            self.sock.sendmsg([struct.pack("ii", self.rank, tag)], anc, 0, self._addr(dst))
         finally:
             for fd in fds:
                 os.close(fd)

@@ -430,6 +430,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("STATUS_TIMEOUT") = (int)kStatusTimeout;
   m.attr("STATUS_POISONED") = (int)kStatusPoisoned;
 
+  // Read / write one 32-bit word at a device address of this process (own or peer-mapped):
+  // used by the bootstrap self-check to prove that a mapping reaches the peer's memory.
+  m.def("peek_u32", [](uint64_t addr) {
+    uint32_t v = 0;
+    PCCL_CUDA(cudaMemcpy(&v, (const void*)addr, 4, cudaMemcpyDeviceToHost));
+    return v;
+  });
+  m.def("poke_u32", [](uint64_t addr, uint32_t v) {
+    PCCL_CUDA(cudaMemcpy((void*)addr, &v, 4, cudaMemcpyHostToDevice));
+    PCCL_CUDA(cudaDeviceSynchronize());
+  });
   m.def("_throw_test", [](int k) {
     if (k == 0) throw pccl::Error("pccl error");
     if (k == 1) TORCH_CHECK(false, "torch check");
@@ -455,7 +466,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   py::class_<VmmSegment>(m, "VmmSegment")
       .def(py::init<int, uint64_t, int>(), py::arg("device"), py::arg("bytes"), py::arg("world_for_multicast") = 0)
-      .def(py::init<int, int, uint64_t>(), py::arg("device"), py::arg("fd"), py::arg("bytes"))
+      // a named factory, not an overload: (device, fd, bytes) and (device, bytes, world) are
+      // both three integers and overload resolution would silently pick the allocating one
+      .def_static("from_fd", [](int device, int fd, uint64_t bytes) { return new VmmSegment(device, fd, bytes); },
+                  py::arg("device"), py::arg("fd"), py::arg("bytes"), py::return_value_policy::take_ownership)
       .def_property_readonly("ptr", &VmmSegment::ptr)
       .def_property_readonly("bytes", &VmmSegment::bytes)
       .def("export_fd", &VmmSegment::export_fd)
