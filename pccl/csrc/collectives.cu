@@ -1,8 +1,7 @@
 // The collective kernels.  One launch runs a whole collective: every step of the ring,
 // recursive doubling/halving or direct schedule happens inside the kernel, with data
-// moving by plain 16-byte loads and stores on peer-mapped memory (NVLink 5 through
-// NVSwitch) or by NVLS multimem instructions, and with system-scope flags in place of the
-// per-step host synchronisation + MPI_Sendrecv of the reference
+// moving over peer-mapped memory (NVLink 5 through NVSwitch) and with system-scope flags
+// in place of the per-step host synchronisation + MPI_Sendrecv of the reference
 // (pccl/src/all_gather.cpp:41-66, pccl/src/reduce_scatter.cpp:50-89 and :127-146).
 //
 // Work is split into LANES: lane c (= blockIdx.x) of every rank handles the same byte or
@@ -10,10 +9,16 @@
 // Lanes never synchronise with one another, so a grid needs no grid-wide barrier and the
 // kernels are persistent with at most one CTA per SM.
 //
+// Bulk data moves through the SM's copy engine (cp.async.bulk through a ring of shared
+// memory stages, bulk.cuh): few lanes keep NVLink busy and the other SMs stay free for the
+// GEMMs of the training step.  Ranges that are not 16-byte aligned use the load/store
+// loops of primitives.cuh.
+//
 // The reference's fp32 vectorAdd launch per step (pccl/src/common.cu:5-19) does not exist
 // here: partial sums are formed in fp32 registers while the data is on its way.
 #include <cuda_runtime.h>
 
+#include "bulk.cuh"
 #include "launch.h"
 #include "primitives.cuh"
 
@@ -23,8 +28,41 @@ namespace {
 
 __device__ __forceinline__ int step_kind(int algo, int t) { return kSlotStep0 + (algo == kDirect ? 0 : t); }
 
+// Copy one range to ndst destinations: copy engine when aligned, thread loops otherwise.
+template <bool REMOTE_SRC>
+__device__ __forceinline__ bool lane_copy(BulkPipe& pipe, char* const* dsts, int ndst, const char* src, uint64_t len) {
+  if (len == 0 || ndst == 0) return true;
+  bool aligned = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && len >= 2048;
+  for (int d = 0; d < ndst; ++d) aligned = aligned && (reinterpret_cast<uintptr_t>(dsts[d]) & 15u) == 0;
+  uint64_t done = 0;
+  if (aligned) {
+    done = len & ~(uint64_t)15;
+    if (!cta_bulk_copy(pipe, dsts, ndst, src, done)) return false;
+  }
+  if (done < len)
+    for (int d = 0; d < ndst; ++d)
+      if (dsts[d] + done != src + done) cta_copy<REMOTE_SRC>(dsts[d] + done, src + done, len - done);
+  return true;
+}
+template <bool REMOTE_SRC>
+__device__ __forceinline__ bool lane_copy1(BulkPipe& pipe, char* dst, const char* src, uint64_t len) {
+  if (dst == src) return true;
+  char* d[1] = {dst};
+  return lane_copy<REMOTE_SRC>(pipe, d, 1, src, len);
+}
+
+// Publish a flag after data: first make sure the copy engine's stores have been performed.
+__device__ __forceinline__ void publish_mask(const GroupDev& g, const LaneCtx& c, int kind, unsigned mask) {
+  cta_bulk_flush();
+  cta_signal_mask(g, c, kind, mask);
+}
+__device__ __forceinline__ void publish(const GroupDev& g, const LaneCtx& c, int kind, int dst) {
+  publish_mask(g, c, kind, 1u << dst);
+}
+
 // ============================================================================ all-gather
 __global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __grid_constant__ AllGatherArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
   const GroupDev& g = a.g;
   const int P = g.size;
   const LaneCtx c{(int)blockIdx.y, g.first_local + (int)blockIdx.y, (int)blockIdx.x, kCollAllGather};
@@ -33,6 +71,8 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __gri
   lane_range(a.sub_bytes, 16, c.lane, gridDim.x, &lo, &hi);
   const uint64_t len = hi - lo;
   if (len == 0) return;  // the same lane is empty on every rank
+  BulkPipe pipe;
+  bulk_pipe_init(pipe, smem, g.timeout_ns);
   const int algo = a.algo;
   char* mine = g.heap[me] + a.recv_off;
   const char* in = a.in[c.li];
@@ -52,22 +92,25 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __gri
   };
 
   if (P == 1) {
-    if (out != nullptr)
-      for (int j = 0; j < a.nsub; ++j) cta_copy<false>(out + opos(0, j), own(j), len);
-    else if (in != nullptr)
-      for (int j = 0; j < a.nsub; ++j) cta_copy<false>(mine + pos(0, j), own(j), len);
+    for (int j = 0; j < a.nsub; ++j) {
+      char* d = out != nullptr ? out + opos(0, j) : mine + pos(0, j);
+      if (!lane_copy1<false>(pipe, d, own(j), len)) return;
+    }
+    cta_bulk_flush();
     return;
   }
 
   if (algo == kPull) {
     // Contributions sit at in_off of every heap; consumers load them.
     char* stage = g.heap[me] + a.in_off;
-    if (in != nullptr)
-      for (int j = 0; j < a.nsub; ++j) cta_copy<false>(stage + (uint64_t)j * a.in_sub_stride + lo, own(j), len);
-    cta_signal_mask(g, c, kSlotEntry, others);
+    if (in != nullptr) {
+      for (int j = 0; j < a.nsub; ++j)
+        if (!lane_copy1<false>(pipe, stage + (uint64_t)j * a.in_sub_stride + lo, own(j), len)) return;
+    }
+    publish_mask(g, c, kSlotEntry, others);
     for (int j = 0; j < a.nsub; ++j) {
       char* d = out != nullptr ? out + opos(me, j) : mine + pos(me, j);
-      cta_copy<false>(d, own(j), len);
+      if (!lane_copy1<false>(pipe, d, own(j), len)) return;
     }
     for (int k = 1; k < P; ++k) {
       const int p = pmod(me + k, P);
@@ -75,10 +118,10 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __gri
       const char* theirs = g.heap[p] + a.in_off;
       for (int j = 0; j < a.nsub; ++j) {
         char* d = out != nullptr ? out + opos(p, j) : mine + pos(p, j);
-        cta_copy<true>(d, theirs + (uint64_t)j * a.in_sub_stride + lo, len);
+        if (!lane_copy1<true>(pipe, d, theirs + (uint64_t)j * a.in_sub_stride + lo, len)) return;
       }
     }
-    cta_signal_mask(g, c, kSlotExit, others);
+    publish_mask(g, c, kSlotExit, others);     // flush: our loads of their memory are complete
     cta_wait_mask(g, c, kSlotExit, others);
     return;
   }
@@ -95,11 +138,26 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __gri
     }
     cta_signal_mask(g, c, kSlotStep0, others);
     if (!cta_wait_mask(g, c, kSlotStep0, others)) return;
-  } else {
-    // Push schedules: direct, ring, recursive doubling.
-    if (in != nullptr)
-      for (int j = 0; j < a.nsub; ++j) cta_copy<false>(mine + pos(me, j), own(j), len);
+  } else if (algo == kDirect) {
+    // One pass over the own block feeds every peer (and the local copies) from one staging read.
     cta_signal_mask(g, c, kSlotEntry, others);
+    if (!cta_wait_mask(g, c, kSlotEntry, others)) return;
+    for (int j = 0; j < a.nsub; ++j) {
+      char* dsts[kMaxRanks + 1];
+      int nd = 0;
+      for (int k = 1; k < P; ++k) dsts[nd++] = g.heap[pmod(me + k, P)] + a.recv_off + pos(me, j);
+      if (in != nullptr) dsts[nd++] = mine + pos(me, j);
+      if (out != nullptr) dsts[nd++] = out + opos(me, j);
+      if (!lane_copy<false>(pipe, dsts, nd, own(j), len)) return;
+    }
+    publish_mask(g, c, kSlotStep0, others);
+    if (!cta_wait_mask(g, c, kSlotStep0, others)) return;
+  } else {
+    // Ring and recursive doubling: forward what has arrived.
+    if (in != nullptr)
+      for (int j = 0; j < a.nsub; ++j)
+        if (!lane_copy1<false>(pipe, mine + pos(me, j), own(j), len)) return;
+    publish_mask(g, c, kSlotEntry, others);      // flush: later steps read the landing zone
     unsigned entered = 0, arrived = 0;
     const int n = num_steps(algo, P);
     for (int t = 0; t < n; ++t) {
@@ -115,32 +173,65 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __gri
       char* theirs = g.heap[s.dst] + a.recv_off;
       for (int b = s.send_first; b < s.send_first + s.nblocks; ++b)
         for (int j = 0; j < a.nsub; ++j) {
-          if (b == me) cta_copy<false>(theirs + pos(b, j), own(j), len);
-          else cta_copy<true>(theirs + pos(b, j), mine + pos(b, j), len);
+          if (b == me) {
+            if (!lane_copy1<false>(pipe, theirs + pos(b, j), own(j), len)) return;
+          } else {
+            if (!lane_copy1<true>(pipe, theirs + pos(b, j), mine + pos(b, j), len)) return;
+          }
         }
-      cta_signal(g, c, step_kind(algo, t), s.dst);
+      publish(g, c, step_kind(algo, t), s.dst);
     }
-    if (algo == kDirect) {
-      if (!cta_wait_mask(g, c, kSlotStep0, others)) return;
-    } else {
-      for (int t = 0; t < n; ++t)
-        if (!((arrived >> t) & 1u))
-          if (!cta_wait(g, c, step_kind(algo, t), ag_step(algo, P, me, t).src)) return;
-    }
+    for (int t = 0; t < n; ++t)
+      if (!((arrived >> t) & 1u))
+        if (!cta_wait(g, c, step_kind(algo, t), ag_step(algo, P, me, t).src)) return;
   }
 
   if (out != nullptr) {
     for (int s = 0; s < P; ++s)
       for (int j = 0; j < a.nsub; ++j) {
-        if (s == me) cta_copy<false>(out + opos(s, j), own(j), len);
-        else cta_copy<true>(out + opos(s, j), mine + pos(s, j), len);
+        if (s == me) {
+          if (algo != kDirect && !lane_copy1<false>(pipe, out + opos(s, j), own(j), len)) return;
+        } else {
+          if (!lane_copy1<true>(pipe, out + opos(s, j), mine + pos(s, j), len)) return;
+        }
       }
   }
+  cta_bulk_flush();
 }
 
 // ============================================================================ reduce-scatter
+// Sum nsrc sources (first one of type TA, the rest TW) into one destination.
+template <int TA, int TW, int TOUT, bool REMOTE_W>
+__device__ __forceinline__ bool lane_reduce(BulkPipe& pipe, char* out, const char* a_src, const char* const* w, int nw,
+                                            uint64_t cnt, float scale) {
+  constexpr uint64_t SA = Elem<TA>::size, SO = Elem<TOUT>::size;
+  uint64_t done = 0;
+  if constexpr (TA == TW) {
+    bool aligned = cnt >= 1024 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(a_src) & 15u) == 0;
+    for (int k = 0; k < nw; ++k) aligned = aligned && (reinterpret_cast<uintptr_t>(w[k]) & 15u) == 0;
+    if (aligned) {
+      const char* srcs[kMaxReduceSrc + 1];
+      int ns = 0;
+      srcs[ns++] = a_src;
+      for (int k = 0; k < nw; ++k) srcs[ns++] = w[k];
+      done = cnt & ~(uint64_t)7;
+      char* o[1] = {out};
+      if (!cta_bulk_reduce<TA, TOUT>(pipe, o, 1, srcs, ns, done, scale)) return false;
+    }
+  }
+  if (done < cnt) {
+    const char* wt[kMaxReduceSrc];
+    for (int k = 0; k < nw; ++k) wt[k] = w[k] + done * Elem<TW>::size;
+    char* o = out + done * SO;
+    cta_reduce<TA, TW, TOUT, REMOTE_W>(&o, 1, a_src + done * SA, wt, nw, cnt - done, scale);
+  }
+  return true;
+}
+
 template <int TIN, int TW, int TOUT>
 __global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const __grid_constant__ ReduceScatterArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
   const GroupDev& g = a.g;
   const int P = g.size;
   const LaneCtx c{(int)blockIdx.y, g.first_local + (int)blockIdx.y, (int)blockIdx.x, kCollReduceScatter};
@@ -149,6 +240,8 @@ __global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const _
   lane_range(a.sub_elems, 8, c.lane, gridDim.x, &lo, &hi);
   const uint64_t cnt = hi - lo;
   if (cnt == 0) return;
+  BulkPipe pipe;
+  bulk_pipe_init(pipe, smem, g.timeout_ns);
   const int algo = a.algo;
   const char* in = a.in[c.li] != nullptr ? a.in[c.li] : g.heap[me] + a.in_off;
   char* out = a.out[c.li];
@@ -179,8 +272,7 @@ __global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const _
       const char* w[kMaxReduceSrc];
       int nw = 0;
       for (int k = 1; k < P; ++k) w[nw++] = in_ptr(g.heap[pmod(me + k, P)] + a.in_off, me, j);
-      char* o = out_ptr(j);
-      cta_reduce<TIN, TIN, TOUT, true>(&o, 1, in_ptr(in, me, j), w, nw, cnt, a.scale);
+      if (!lane_reduce<TIN, TIN, TOUT, true>(pipe, out_ptr(j), in_ptr(in, me, j), w, nw, cnt, a.scale)) return;
     }
     cta_signal_mask(g, c, kSlotExit, others);
     cta_wait_mask(g, c, kSlotExit, others);
@@ -251,14 +343,16 @@ __global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const _
           }
         if (t < n) {
           char* d = stage_ptr(s.dst, rs_stage_offset(algo, P, t) + (b - s.send_first), j);
-          if (nw == 0 && TW == TIN) cta_copy<false>(d, in_ptr(in, b, j), cnt * SI);
-          else cta_reduce<TIN, TW, TW, true>(&d, 1, in_ptr(in, b, j), w, nw, cnt, 1.0f);
+          if (nw == 0 && TW == TIN) {
+            if (!lane_copy1<false>(pipe, d, in_ptr(in, b, j), cnt * SI)) return;
+          } else {
+            cta_reduce<TIN, TW, TW, true>(&d, 1, in_ptr(in, b, j), w, nw, cnt, 1.0f);
+          }
         } else {
-          char* o = out_ptr(j);
-          cta_reduce<TIN, TW, TOUT, true>(&o, 1, in_ptr(in, b, j), w, nw, cnt, a.scale);
+          if (!lane_reduce<TIN, TW, TOUT, true>(pipe, out_ptr(j), in_ptr(in, b, j), w, nw, cnt, a.scale)) return;
         }
       }
-    if (t < n) cta_signal(g, c, step_kind(algo, t), s.dst);
+    if (t < n) publish(g, c, step_kind(algo, t), s.dst);
   }
 }
 
@@ -269,6 +363,7 @@ __global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const _
 // pccl/src/yacl.cpp:146-177 of the reference does with two temporaries and two host loops.
 template <int DT>
 __global__ void __launch_bounds__(kCollThreads, 1) all_reduce_kernel(const __grid_constant__ AllReduceArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
   const GroupDev& g = a.g;
   const int P = g.size;
   const LaneCtx c{(int)blockIdx.y, g.first_local + (int)blockIdx.y, (int)blockIdx.x, kCollAllReduce};
@@ -278,6 +373,8 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_reduce_kernel(const __gri
   char* data = a.data[c.li];
   char* buf = g.heap[me] + a.buf_off;
   const unsigned others = others_mask(P, me);
+  BulkPipe pipe;
+  bulk_pipe_init(pipe, smem, g.timeout_ns);
 
   auto slice = [&](int s, uint64_t* lo, uint64_t* cnt) {
     uint64_t b = (uint64_t)s * per, e = b + per;
@@ -301,9 +398,9 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_reduce_kernel(const __gri
     for (int s = 0; s < P; ++s) {
       uint64_t lo, cnt;
       slice(s, &lo, &cnt);
-      cta_copy<false>(buf + lo * S, data + lo * S, cnt * S);
+      if (!lane_copy1<false>(pipe, buf + lo * S, data + lo * S, cnt * S)) return;
     }
-  cta_signal_mask(g, c, kSlotEntry, others);
+  publish_mask(g, c, kSlotEntry, others);
   if (!cta_wait_mask(g, c, kSlotEntry, others)) return;
 
   uint64_t lo, cnt;
@@ -347,12 +444,14 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_reduce_kernel(const __gri
     for (int s = 0; s < P; ++s) {
       uint64_t l2, c2;
       slice(s, &l2, &c2);
-      cta_copy<true>(data + l2 * S, buf + l2 * S, c2 * S);
+      if (!lane_copy1<true>(pipe, data + l2 * S, buf + l2 * S, c2 * S)) return;
     }
+  cta_bulk_flush();
 }
 
 // ============================================================================ broadcast
 __global__ void __launch_bounds__(kCollThreads, 1) broadcast_kernel(const __grid_constant__ BroadcastArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
   const GroupDev& g = a.g;
   const int P = g.size;
   const LaneCtx c{(int)blockIdx.y, g.first_local + (int)blockIdx.y, (int)blockIdx.x, kCollBroadcast};
@@ -362,6 +461,8 @@ __global__ void __launch_bounds__(kCollThreads, 1) broadcast_kernel(const __grid
   lane_range(a.bytes, 16, c.lane, gridDim.x, &lo, &hi);
   const uint64_t len = hi - lo;
   if (len == 0) return;
+  BulkPipe pipe;
+  bulk_pipe_init(pipe, smem, g.timeout_ns);
   char* data = a.data[c.li];
   char* buf = g.heap[me] + a.buf_off;
   const unsigned others = others_mask(P, me);
@@ -372,13 +473,17 @@ __global__ void __launch_bounds__(kCollThreads, 1) broadcast_kernel(const __grid
       char* mc = g.mc_heap + a.buf_off + lo;
       for (uint64_t i = threadIdx.x; i < (len >> 4); i += blockDim.x) multimem_st_v4(mc + (i << 4), ld_v4(src + lo + (i << 4)));
     } else {
-      for (int k = 1; k < P; ++k) cta_copy<false>(g.heap[pmod(me + k, P)] + a.buf_off + lo, src + lo, len);
+      char* dsts[kMaxRanks];
+      int nd = 0;
+      for (int k = 1; k < P; ++k) dsts[nd++] = g.heap[pmod(me + k, P)] + a.buf_off + lo;
+      if (!lane_copy<false>(pipe, dsts, nd, src + lo, len)) return;
     }
-    cta_signal_mask(g, c, kSlotStep0, others);
+    publish_mask(g, c, kSlotStep0, others);
   } else {
     cta_signal(g, c, kSlotEntry, a.root);
     if (!cta_wait(g, c, kSlotStep0, a.root)) return;
-    if (data != nullptr) cta_copy<true>(data + lo, buf + lo, len);
+    if (data != nullptr && !lane_copy1<true>(pipe, data + lo, buf + lo, len)) return;
+    cta_bulk_flush();
   }
 }
 
@@ -393,26 +498,31 @@ __global__ void __launch_bounds__(64, 1) barrier_kernel(const __grid_constant__ 
 }
 
 template <typename Args>
-cudaError_t launch(void (*kernel)(const Args), const Args& args, int nlanes, int threads, cudaStream_t stream) {
+cudaError_t launch(void (*kernel)(const Args), const Args& args, int nlanes, int threads, size_t smem, cudaStream_t stream) {
   dim3 grid(nlanes, args.g.nlocal), block(threads);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return e;
+  }
   if (args.g.nlocal > 1) {
     // Several ranks in one launch wait on one another: every CTA must be resident.
     void* params[] = {const_cast<Args*>(&args)};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, block, params, 0, stream);
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, block, params, smem, stream);
   }
-  kernel<<<grid, block, 0, stream>>>(args);
+  kernel<<<grid, block, smem, stream>>>(args);
   return cudaGetLastError();
 }
 
 }  // namespace
 
 cudaError_t launch_all_gather(const AllGatherArgs& a, int nlanes, cudaStream_t stream) {
-  return launch(all_gather_kernel, a, nlanes, kCollThreads, stream);
+  return launch(all_gather_kernel, a, nlanes, kCollThreads, kBulkSmemBytes, stream);
 }
 
 #define PCCL_RS_CASE(TI, TW_, TO)                                                              \
   if (a.in_dtype == TI && a.wire_dtype == TW_ && a.out_dtype == TO)                            \
-    return launch(reduce_scatter_kernel<TI, TW_, TO>, a, nlanes, kCollThreads, stream);
+    return launch(reduce_scatter_kernel<TI, TW_, TO>, a, nlanes, kCollThreads, kBulkSmemBytes, stream);
 
 cudaError_t launch_reduce_scatter(const ReduceScatterArgs& a, int nlanes, cudaStream_t stream) {
   PCCL_RS_CASE(kBF16, kBF16, kBF16)
@@ -429,24 +539,28 @@ cudaError_t launch_reduce_scatter(const ReduceScatterArgs& a, int nlanes, cudaSt
 }
 
 cudaError_t launch_all_reduce(const AllReduceArgs& a, int nlanes, cudaStream_t stream) {
-  if (a.dtype == kBF16) return launch(all_reduce_kernel<kBF16>, a, nlanes, kCollThreads, stream);
-  if (a.dtype == kF16) return launch(all_reduce_kernel<kF16>, a, nlanes, kCollThreads, stream);
-  if (a.dtype == kF32) return launch(all_reduce_kernel<kF32>, a, nlanes, kCollThreads, stream);
+  if (a.dtype == kBF16) return launch(all_reduce_kernel<kBF16>, a, nlanes, kCollThreads, kBulkSmemBytes, stream);
+  if (a.dtype == kF16) return launch(all_reduce_kernel<kF16>, a, nlanes, kCollThreads, kBulkSmemBytes, stream);
+  if (a.dtype == kF32) return launch(all_reduce_kernel<kF32>, a, nlanes, kCollThreads, kBulkSmemBytes, stream);
   return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_broadcast(const BroadcastArgs& a, int nlanes, cudaStream_t stream) {
-  return launch(broadcast_kernel, a, nlanes, kCollThreads, stream);
+  return launch(broadcast_kernel, a, nlanes, kCollThreads, kBulkSmemBytes, stream);
 }
 
 cudaError_t launch_barrier(const BarrierArgs& a, cudaStream_t stream) {
-  return launch(barrier_kernel, a, 1, 64, stream);
+  return launch(barrier_kernel, a, 1, 64, 0, stream);
 }
 
 int max_resident_lanes(int device) {
   int sms = 0, per_sm = 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, all_gather_kernel, kCollThreads, 0) != cudaSuccess) return 0;
+  if (cudaFuncSetAttribute(reinterpret_cast<const void*>(all_gather_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)kBulkSmemBytes) != cudaSuccess)
+    return 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, all_gather_kernel, kCollThreads, kBulkSmemBytes) != cudaSuccess)
+    return 0;
   int m = sms * (per_sm > 0 ? 1 : 0);  // the kernels are written for one CTA per SM
   return m > kMaxLanes ? kMaxLanes : m;
 }

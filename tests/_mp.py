@@ -36,15 +36,25 @@ def run_ranks(fn, world, port, args=(), backend="gloo", timeout=120):
     procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, backend, errq)) for r in range(world)]
     for p in procs:
         p.start()
+    import queue as _queue
+
     results = []
+    timed_out = False
     try:
         for _ in range(world):
-            results.append(errq.get(timeout=timeout))
+            try:
+                # once one rank has failed, its peers are probably stuck in a collective: do not wait long
+                failed = any(tb is not None for _r, tb in results)
+                results.append(errq.get(timeout=15 if failed else timeout))
+            except _queue.Empty:
+                timed_out = True
+                break
     finally:
         for p in procs:
-            p.join(timeout=10)
+            p.join(timeout=1 if timed_out else 10)
             if p.is_alive():
                 p.kill()   # exact child we started
     failures = [f"rank {r}:\n{tb}" for r, tb in results if tb is not None]
     assert not failures, "\n".join(failures)
+    assert not timed_out, f"only {len(results)} of {world} ranks finished within the time limit"
     assert len(results) == world
