@@ -45,6 +45,9 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=None)
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--algorithm", default="auto")
+    ap.add_argument("--lanes", type=int, default=int(os.environ.get("PCCL_TRAIN_LANES", "16")),
+                    help="SMs a parameter gather / gradient reduction may occupy while it overlaps the GEMMs")
+    ap.add_argument("--nvls", type=int, default=int(os.environ.get("PCCL_ENABLE_NVLS", "0")))
     ap.add_argument("--fused-ag-gemm", type=int, default=int(os.environ.get("PCCL_FUSED_AG_GEMM", "0")))
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -94,10 +97,10 @@ def main() -> None:
     comm = None
     if args.impl == "pccl":
         heap = heap_bytes_needed(cfg, world) + (320 << 20)
-        comm = pccl.init(heap_bytes=heap, staging_bytes=64 << 20)
+        comm = pccl.init(heap_bytes=heap, staging_bytes=64 << 20, enable_nvls=bool(args.nvls))
         from pccl.patch_deepspeed import patch_deepspeed
 
-        patch_deepspeed(world, algorithm=args.algorithm)
+        patch_deepspeed(world, algorithm=args.algorithm, lanes=args.lanes)
     backend = TorchBackend()
     linear_fwd = None
     if args.impl == "pccl" and args.fused_ag_gemm:
@@ -188,7 +191,8 @@ def main() -> None:
                 "ffn": cfg.d_ff, "vocab": cfg.vocab, "params": cfg.num_params(),
                 "global_batch": world * mb, "micro_batch_per_gpu": mb, "seq_len": S,
                 "parallelism": f"zero3-dp{world}", "optimizer": "AdamW fp32 master+moments, grad-norm clip 1.0",
-                "algorithm": args.algorithm, "fused_ag_gemm": bool(args.fused_ag_gemm),
+                "algorithm": args.algorithm, "lanes": args.lanes, "nvls": bool(args.nvls),
+                "fused_ag_gemm": bool(args.fused_ag_gemm),
                 "l2": "working set per step (tens of GB) exceeds the 126 MB L2; no explicit flush",
                 "transport": comm.transport_name if comm is not None else "nccl",
             },

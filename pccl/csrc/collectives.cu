@@ -28,11 +28,15 @@ namespace {
 
 __device__ __forceinline__ int step_kind(int algo, int t) { return kSlotStep0 + (algo == kDirect ? 0 : t); }
 
+// Below this many bytes per lane the copy-engine pipeline costs more (barrier set-up, first
+// load latency) than it saves; the thread loops take over.
+constexpr uint64_t kBulkMinBytes = 192 * 1024;
+
 // Copy one range to ndst destinations: copy engine when aligned, thread loops otherwise.
 template <bool REMOTE_SRC>
 __device__ __forceinline__ bool lane_copy(BulkPipe& pipe, char* const* dsts, int ndst, const char* src, uint64_t len) {
   if (len == 0 || ndst == 0) return true;
-  bool aligned = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && len >= 2048;
+  bool aligned = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && len >= kBulkMinBytes;
   for (int d = 0; d < ndst; ++d) aligned = aligned && (reinterpret_cast<uintptr_t>(dsts[d]) & 15u) == 0;
   uint64_t done = 0;
   if (aligned) {
@@ -134,7 +138,17 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __gri
       const char* s = own(j);
       char* d = g.mc_heap + a.recv_off + pos(me, j);
       const uint64_t nvec = len >> 4;
-      for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) multimem_st_v4(d + (i << 4), ld_v4(s + (i << 4)));
+      constexpr int U = 8;
+      const uint64_t nt = blockDim.x;
+      uint64_t i = threadIdx.x;
+      for (; i + (U - 1) * nt < nvec; i += U * nt) {
+        uint4 v[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) v[k] = ld_v4(s + ((i + k * nt) << 4));
+#pragma unroll
+        for (int k = 0; k < U; ++k) multimem_st_v4(d + ((i + k * nt) << 4), v[k]);
+      }
+      for (; i < nvec; i += nt) multimem_st_v4(d + (i << 4), ld_v4(s + (i << 4)));
     }
     cta_signal_mask(g, c, kSlotStep0, others);
     if (!cta_wait_mask(g, c, kSlotStep0, others)) return;
@@ -207,7 +221,7 @@ __device__ __forceinline__ bool lane_reduce(BulkPipe& pipe, char* out, const cha
   constexpr uint64_t SA = Elem<TA>::size, SO = Elem<TOUT>::size;
   uint64_t done = 0;
   if constexpr (TA == TW) {
-    bool aligned = cnt >= 1024 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
+    bool aligned = cnt * SA >= kBulkMinBytes && (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
                    (reinterpret_cast<uintptr_t>(a_src) & 15u) == 0;
     for (int k = 0; k < nw; ++k) aligned = aligned && (reinterpret_cast<uintptr_t>(w[k]) & 15u) == 0;
     if (aligned) {
@@ -288,8 +302,7 @@ __global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const _
       const char* src = in_ptr(g.mc_heap + a.in_off, me, j);
       char* o = out_ptr(j);
       const uint64_t nvec = cnt / EPV;
-      for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-        const uint4 v = multimem_ld_reduce_v4<TIN>(src + (i << 4));
+      auto emit = [&](uint64_t i, const uint4& v) {
         float f[8];
         if constexpr (TIN == kF32) {
           f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
@@ -297,8 +310,30 @@ __global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const _
           Elem<TIN>::unpack(v, f);
         }
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) Elem<TOUT>::store1(o + (i * EPV + e) * SO, f[e] * a.scale);
+        for (int e = 0; e < EPV; ++e) f[e] *= a.scale;
+        char* dst = o + i * EPV * SO;
+        if constexpr (TOUT == kF32) {
+          st_v4(dst, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
+          if constexpr (EPV == 8)
+            st_v4(dst + 16, make_uint4(__float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7])));
+        } else if constexpr (EPV == 8) {
+          st_v4(dst, Elem<TOUT>::pack(f));
+        } else {
+#pragma unroll
+          for (int e = 0; e < EPV; ++e) Elem<TOUT>::store1(dst + e * SO, f[e]);
+        }
+      };
+      constexpr int U = 8;     // switch-side reductions in flight per thread
+      const uint64_t nt = blockDim.x;
+      uint64_t i = threadIdx.x;
+      for (; i + (U - 1) * nt < nvec; i += U * nt) {
+        uint4 v[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) v[k] = multimem_ld_reduce_v4<TIN>(src + ((i + k * nt) << 4));
+#pragma unroll
+        for (int k = 0; k < U; ++k) emit(i + k * nt, v[k]);
       }
+      for (; i < nvec; i += nt) emit(i, multimem_ld_reduce_v4<TIN>(src + (i << 4)));
     }
     cta_signal_mask(g, c, kSlotExit, others);
     cta_wait_mask(g, c, kSlotExit, others);
@@ -501,9 +536,16 @@ template <typename Args>
 cudaError_t launch(void (*kernel)(const Args), const Args& args, int nlanes, int threads, size_t smem, cudaStream_t stream) {
   dim3 grid(nlanes, args.g.nlocal), block(threads);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
-    if (e != cudaSuccess) return e;
+    // once per kernel and device (the attribute belongs to the function in the current context)
+    static thread_local const void* configured[64] = {nullptr};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || configured[dev] != reinterpret_cast<const void*>(kernel)) {
+      cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) configured[dev] = reinterpret_cast<const void*>(kernel);
+    }
   }
   if (args.g.nlocal > 1) {
     // Several ranks in one launch wait on one another: every CTA must be resident.

@@ -1,0 +1,42 @@
+// Blackwell GEMM and fused all-gather+GEMM (gemm_sm100.cu).
+//
+//   C[M,N] = A[M,K] * W[N,K]^T (+ bias[N])      bf16 in, fp32 accumulation in TMEM, bf16 out
+//
+// Plain mode: W is one [N,K] matrix in local memory.
+// Fused mode: W is sharded by rows over the P members of a group (member p owns rows
+// [p*N/P, (p+1)*N/P) in its symmetric heap).  The same kernel gathers the shards into a
+// local [N,K] buffer over NVLink (a few "gatherer" CTAs driving the copy engine, one flag
+// per 256-row panel) and multiplies: tiles whose panel is local start at once, the others
+// as their panel lands.  The gathered matrix stays in the local buffer for later use.
+//
+// The reference has no GEMM at all; this is the "parameter all-gather fused with the
+// first GEMM that consumes the gathered shard" of the ZeRO-3 path
+// (hook point: pccl/patch_deepspeed.py:29-40 of the reference).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "device_types.h"
+
+namespace pccl {
+
+constexpr int kGemmBM = 128, kGemmBN = 256, kGemmBK = 64;
+
+struct GemmArgs {
+  int M, N, K;
+  const void* A;        // [M,K] bf16 row-major, 16-byte aligned, K % 8 == 0
+  const void* W;        // [N,K] bf16 row-major (plain mode: the weight; fused mode: the local gather buffer)
+  void* C;              // [M,N] bf16 row-major, N % 8 == 0
+  const void* bias;     // [N] bf16 or nullptr
+  int* error;           // device int, set non-zero when a bounded wait ran out
+  // ---- fused all-gather (gather_ctas == 0: plain GEMM)
+  int gather_ctas;      // CTAs that move shards instead of multiplying
+  GroupDev g;           // group, epoch, flags (filled by Comm::begin_call)
+  uint64_t shard_off;   // offset of the [N/P, K] shard inside every member's heap
+  uint32_t* panel_flags;  // device, ceil(N/256) counters, zeroed before the launch
+};
+
+// Launches on `stream`.  Returns cudaErrorInvalidValue for shapes the kernel does not take.
+cudaError_t launch_gemm_sm100(const GemmArgs& a, int sm_count, cudaStream_t stream);
+
+}  // namespace pccl

@@ -1,0 +1,456 @@
+// tcgen05 / TMEM / TMA GEMM for sm_100a, with an optional in-kernel all-gather of the
+// weight (see gemm.h for the operation).
+//
+// Persistent kernel, one CTA per SM, 192 threads:
+//   warp 0      TMA producer: A and W tiles (128x64, 256x64 bf16, 128-byte swizzle) into a
+//               4-stage shared-memory ring; plain tiled TMA loads, no cluster multicast
+//   warp 1      allocates TMEM, issues tcgen05.mma (M128 N256 K16, cta_group::1) from one
+//               elected thread; tcgen05.commit releases ring stages and publishes accumulators
+//   warps 2-5   epilogue: tcgen05.ld 32x32b from TMEM, bias, bf16, 16-byte stores
+// Two 128x256 fp32 accumulators (all 512 TMEM columns) let the epilogue of one tile overlap
+// the main loop of the next.
+//
+// Fused mode: the first `gather_ctas` CTAs do not multiply; they pull 256-row panels of the
+// peers' weight shards into the local buffer with the copy engine (bulk.cuh) and raise one
+// flag per panel.  The producer of a GEMM CTA waits for the panel's flag before its TMA
+// loads read the panel from LOCAL memory; panels of the own shard are read directly from
+// the shard, so the math starts immediately.  Remote data crosses NVLink exactly once.
+//
+// Every wait (mbarrier, panel flag, peer flag) is bounded; on expiry the kernel records an
+// error code, lets the other roles drain, frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "bulk.cuh"
+#include "gemm.h"
+#include "primitives.cuh"
+
+namespace pccl {
+
+namespace {
+
+constexpr int BM = kGemmBM, BN = kGemmBN, BK = kGemmBK;
+constexpr int kStages = 4;
+constexpr uint32_t kABytes = BM * BK * 2;            // 16 KiB
+constexpr uint32_t kBBytes = BN * BK * 2;            // 32 KiB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;  // 48 KiB
+constexpr uint32_t kBarOff = kStages * kStageBytes;  // 196,608
+constexpr uint32_t kGemmSmem = kBarOff + 256 + 1024; // barriers + slack for 1 KiB alignment
+constexpr int kGemmThreads = 192;
+constexpr uint64_t kWaitNs = 4ull * 1000 * 1000 * 1000;
+constexpr uint32_t kTmemCols = 512;
+
+static_assert(kBulkSmemBytes <= kBarOff + 256, "the gatherer's copy ring must fit into the GEMM's shared memory");
+
+// ---- error codes written to *error
+constexpr int kErrProducer = 1, kErrMma = 2, kErrEpilogue = 3, kErrPanel = 4, kErrGather = 5;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Bounded wait that also gives up when another role has failed.
+__device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t it = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++it & 255u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > kWaitNs) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart, descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address
+  d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset
+  d |= (uint64_t)1 << 46;                              // version
+  d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+struct TileSched {
+  int tiles_m, tiles_n, total;
+  int tiles_per_rank, P, me;   // fused mode: own panels first, then the peers' in arrival order
+  __device__ __forceinline__ void decode(int t, int* m_idx, int* n_idx) const {
+    const int q = t / tiles_m;
+    *m_idx = t - q * tiles_m;
+    if (tiles_per_rank > 0) {
+      const int r = (me + q / tiles_per_rank) % P;
+      *n_idx = r * tiles_per_rank + q % tiles_per_rank;
+    } else {
+      *n_idx = q;
+    }
+  }
+};
+
+// ---------------------------------------------------------------- gatherer CTAs
+__device__ void gather_role(const GemmArgs& a, unsigned char* smem, int gi) {
+  const GroupDev& g = a.g;
+  const int P = g.size, me = g.first_local;
+  const bool flag_sync = g.sig[0] != nullptr;
+  const LaneCtx c{0, me, gi, kCollAgGemm};
+  BulkPipe pipe;
+  bulk_pipe_init(pipe, smem, g.timeout_ns);
+  const int tpr = (a.N / P) / BN;
+  const uint64_t panel_bytes = (uint64_t)BN * a.K * 2;
+  const unsigned others = others_mask(P, me);
+  char* w_full = reinterpret_cast<char*>(const_cast<void*>(a.W));
+  if (flag_sync) cta_signal_mask(g, c, kSlotEntry, others);
+  unsigned entered = 0;
+  bool ok = true;
+  // remote panels in the order in which the GEMM CTAs want them, dealt round-robin
+  const int nremote = (P - 1) * tpr;
+  for (int i = gi; i < nremote + tpr && ok; i += a.gather_ctas) {
+    // the last tpr entries are the own shard's panels (lowest priority: the GEMM reads them from the shard)
+    const int k = i < nremote ? 1 + i / tpr : 0;
+    const int j = i < nremote ? i % tpr : i - nremote;
+    const int p = (me + k) % P;
+    if (flag_sync && k != 0 && !((entered >> p) & 1u)) {
+      if (!cta_wait(g, c, kSlotEntry, p)) {
+        ok = false;
+        break;
+      }
+      entered |= 1u << p;
+    }
+    const int n_tile = p * tpr + j;
+    char* dst = w_full + (uint64_t)n_tile * panel_bytes;
+    const char* src = g.heap[p] + a.shard_off + (uint64_t)j * panel_bytes;
+    char* d[1] = {dst};
+    if (!cta_bulk_copy(pipe, d, 1, src, panel_bytes)) {
+      ok = false;
+      break;
+    }
+    cta_bulk_flush();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      atomicAdd(a.panel_flags + n_tile, 1u);
+    }
+  }
+  if (!ok && threadIdx.x == 0) atomicCAS(a.error, 0, kErrGather);
+  if (flag_sync) {
+    cta_signal_mask(g, c, kSlotExit, others);   // I no longer read your shard
+    cta_wait_mask(g, c, kSlotExit, others);     // nobody reads mine any more
+  }
+}
+
+// ---------------------------------------------------------------- the kernel
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+                      const __grid_constant__ CUtensorMap tmWown, const __grid_constant__ GemmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  if ((int)blockIdx.x < a.gather_ctas) {
+    gather_role(a, smem, (int)blockIdx.x);
+    return;
+  }
+  const int cta = (int)blockIdx.x - a.gather_ctas, ncta = (int)gridDim.x - a.gather_ctas;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kBarOff);
+  uint64_t* empty = full + kStages;
+  uint64_t* tmem_full = empty + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tmem_full + i, 1);
+      mbar_init(tmem_empty + i, 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  TileSched sch;
+  sch.tiles_m = (a.M + BM - 1) / BM;
+  sch.tiles_n = (a.N + BN - 1) / BN;
+  sch.total = sch.tiles_m * sch.tiles_n;
+  sch.P = a.g.size;
+  sch.me = a.g.first_local;
+  sch.tiles_per_rank = a.gather_ctas > 0 ? (a.N / sch.P) / BN : 0;
+  const int nkb = (a.K + BK - 1) / BK;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ TMA producer
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = cta; t < sch.total && ok; t += ncta) {
+      int m_idx, n_idx;
+      sch.decode(t, &m_idx, &n_idx);
+      const CUtensorMap* wmap = &tmW;
+      int wy = n_idx * BN;
+      if (sch.tiles_per_rank > 0) {
+        const int owner = n_idx / sch.tiles_per_rank;
+        if (owner == sch.me) {
+          wmap = &tmWown;                                   // straight from the shard
+          wy = (n_idx - owner * sch.tiles_per_rank) * BN;
+        } else {
+          // wait until a gatherer has landed this panel in the local buffer
+          const uint32_t* flag = a.panel_flags + n_idx;
+          const uint64_t t0 = global_timer_ns();
+          uint32_t spins = 0;
+          for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v != 0) break;
+            if ((++spins & 63u) == 0u) {
+              if (*abort_flag != 0 || global_timer_ns() - t0 > kWaitNs) {
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+          }
+          if (!ok) {
+            atomicCAS(a.error, 0, kErrPanel);
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");  // flag came through the generic proxy
+        }
+      }
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+        if (!gemm_wait(empty + s, ph ^ 1u, abort_flag)) {
+          ok = false;
+          atomicCAS(a.error, 0, kErrProducer);
+          break;
+        }
+        unsigned char* sa = smem + (size_t)s * kStageBytes;
+        mbar_expect_tx(full + s, kStageBytes);
+        tma_load_2d(sa, &tmA, kb * BK, m_idx * BM, full + s);
+        tma_load_2d(sa + kABytes, wmap, kb * BK, wy, full + s);
+      }
+    }
+    if (!ok) *abort_flag = 1;
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    uint32_t it = 0, tile_count = 0;
+    bool ok = true;
+    for (int t = cta; t < sch.total && ok; t += ncta, ++tile_count) {
+      const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
+      if (!gemm_wait(tmem_empty + acc, acc_ph ^ 1u, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+        if (!gemm_wait(full + s, ph, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes);
+        const uint64_t da = smem_desc(sa), db = smem_desc(sa + kABytes);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          mma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb > 0 || k > 0) ? 1u : 0u);
+        mma_commit(empty + s);             // the stage is free once these MMAs have read it
+      }
+      if (!ok) break;
+      mma_commit(tmem_full + acc);         // accumulator complete
+    }
+    if (!ok) {
+      atomicCAS(a.error, 0, kErrMma);
+      *abort_flag = 1;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------ epilogue
+    uint32_t tile_count = 0;
+    bool ok = true;
+    const int lane_base = (warp & 3) * 32;
+    __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(a.C);
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
+    for (int t = cta; t < sch.total && ok; t += ncta, ++tile_count) {
+      int m_idx, n_idx;
+      sch.decode(t, &m_idx, &n_idx);
+      const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
+      if (!gemm_wait(tmem_full + acc, acc_ph, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = m_idx * BM + lane_base + lane;
+      const uint32_t t_base = tmem_base + acc * BN + ((uint32_t)lane_base << 16);
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld32(t_base + cc * 32, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int col0 = n_idx * BN + cc * 32;
+        if (row < a.M && col0 < a.N) {
+          __nv_bfloat16* out = C + (size_t)row * a.N + col0;
+          if (col0 + 32 <= a.N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
+                if (bias != nullptr) {
+                  x0 += __bfloat162float(bias[col0 + v * 8 + 2 * e]);
+                  x1 += __bfloat162float(bias[col0 + v * 8 + 2 * e + 1]);
+                }
+                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                w[e] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(out + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (col0 + e < a.N) {
+                float x = __uint_as_float(r[e]);
+                if (bias != nullptr) x += __bfloat162float(bias[col0 + e]);
+                out[e] = __float2bfloat16_rn(x);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty + acc);
+    }
+    if (!ok && lane == 0) {
+      atomicCAS(a.error, 0, kErrEpilogue);
+      *abort_flag = 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeFn>(p);
+  }
+  return fn;
+}
+
+// [rows, K] bf16 row-major, box = box_rows x 64 elements, 128-byte swizzle, zero fill.
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {K, rows};
+  cuuint64_t strides[1] = {K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_sm100(const GemmArgs& a, int sm_count, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K % 8) != 0 || (a.N % 8) != 0) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.C)) & 15u)
+    return cudaErrorInvalidValue;
+  const void* own = a.W;
+  uint64_t own_rows = (uint64_t)a.N;
+  if (a.gather_ctas > 0) {
+    const int P = a.g.size;
+    if (P < 1 || a.N % (P * BN) != 0 || a.gather_ctas >= sm_count || a.panel_flags == nullptr) return cudaErrorInvalidValue;
+    own = a.g.heap[a.g.first_local] + a.shard_off;
+    own_rows = (uint64_t)a.N / P;
+    if (reinterpret_cast<uintptr_t>(own) & 15u) return cudaErrorInvalidValue;
+  }
+  CUtensorMap tmA, tmW, tmWown;
+  if (!make_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM)) return cudaErrorInvalidValue;
+  if (!make_map(&tmW, a.W, (uint64_t)a.N, (uint64_t)a.K, BN)) return cudaErrorInvalidValue;
+  if (!make_map(&tmWown, own, own_rows, (uint64_t)a.K, BN)) return cudaErrorInvalidValue;
+  static thread_local bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+  int grid = sm_count;
+  if (a.gather_ctas == 0 && tiles < grid) grid = tiles;
+  gemm_sm100_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(tmA, tmW, tmWown, a);
+  return cudaGetLastError();
+}
+
+}  // namespace pccl

@@ -1,0 +1,71 @@
+"""Fused parameter all-gather + GEMM.
+
+``AllGatherLinear`` holds a weight sharded by rows over a group (each rank owns ``N/P``
+rows in the symmetric heap).  ``forward(x)`` launches ONE kernel that pulls the peers'
+shards over NVLink into a local ``[N, K]`` buffer while it multiplies: output tiles whose
+weight rows are local start at once, the others as their 256-row panel lands.  Afterwards
+the gathered weight is available in ``w_full`` (the backward pass of a ZeRO-3 step reuses
+or re-gathers it).
+
+This is the B200 counterpart of what the reference does at its DeepSpeed hook
+(``pccl/patch_deepspeed.py:29-40``): there the gather is a blocking collective and the GEMM
+that consumes the parameters starts only after it.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+
+from ..comm import Communicator, Group
+
+
+def _C():
+    from .. import build_kernels
+
+    return build_kernels.load()
+
+
+class AllGatherLinear:
+    def __init__(self, comm: Communicator, group: Optional[Group], out_features: int, in_features: int,
+                 gather_ctas: int = 16, device=None):
+        self.comm = comm
+        self.group = group or comm.world_group
+        P = self.group.size
+        if out_features % (P * 256) != 0:
+            raise ValueError(f"out_features must be a multiple of 256 * group size ({256 * P})")
+        if in_features % 8 != 0:
+            raise ValueError("in_features must be a multiple of 8")
+        self.N, self.K, self.P = out_features, in_features, P
+        self.gather_ctas = gather_ctas
+        self.w_shard = comm.empty((out_features // P, in_features), torch.bfloat16)
+        dev = device or self.w_shard.device
+        self.w_full = torch.empty((out_features, in_features), dtype=torch.bfloat16, device=dev)
+
+    def forward(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, check: bool = False) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.K)
+        y, err = _C().ag_gemm(self.comm.native, self.group.gid, x2, self.w_shard, self.w_full, bias, None,
+                              self.gather_ctas)
+        if check:
+            code = int(err.item())
+            self.comm.check(sync=False)
+            if code != 0:
+                raise RuntimeError(f"fused all-gather+GEMM gave up in a bounded wait (code {code})")
+        return y.view(*lead, self.N)
+
+    __call__ = forward
+
+
+def make_linear_fwd(comm: Communicator) -> Callable:
+    """Forward hook for ``pccl.models.gpt.layer_forward``: QKV and FC1, the two GEMMs that
+    consume freshly gathered weights, run on the tcgen05 kernel; everything else stays on
+    the default path."""
+    from .gemm import linear
+
+    def linear_fwd(x, w, b, which):
+        if which in ("qkv", "fc1") and x.dtype == torch.bfloat16 and w.is_contiguous():
+            return linear(x, w, b)
+        return torch.nn.functional.linear(x, w, b)
+
+    return linear_fwd

@@ -55,7 +55,7 @@ def _is_sum(op) -> bool:
 def patched_all_gather(self, output_tensor, input_tensor, group=None, async_op=False):
     if is_global_pg(group):
         return all_gather_2D(output_tensor.view(-1), input_tensor.view(-1), group=get_heir_pg(), async_op=async_op,
-                             use_rd=True, use_pccl_cpp_backend=True, algorithm=_algo)
+                             use_rd=True, use_pccl_cpp_backend=True, algorithm=_algo, lanes=_lanes)
     return self.old_all_gather_into_tensor(output_tensor, input_tensor, group, async_op)
 
 
@@ -63,7 +63,7 @@ def patched_reduce_scatter(self, output_tensor, input_tensor, op=dist.ReduceOp.S
                            scale: float = 1.0):
     if is_global_pg(group) and _is_sum(op):
         return reduce_scatter_2D(output_tensor.view(-1), input_tensor.view(-1), group=get_heir_pg(), async_op=async_op,
-                                 use_rh=True, use_pccl_cpp_backend=True, algorithm=_algo, scale=scale)
+                                 use_rh=True, use_pccl_cpp_backend=True, algorithm=_algo, scale=scale, lanes=_lanes)
     assert scale == 1.0, "scale= is only fused on the library path"
     return self.old_reduce_scatter_tensor(output_tensor, input_tensor, op, group, async_op)
 
@@ -87,6 +87,7 @@ def patched_barrier(self, group=dist.GroupMember.WORLD, async_op=False, device_i
 
 
 _algo: Optional[str] = None
+_lanes: Optional[int] = None
 
 _HOOKS = (
     ("all_gather_into_tensor", patched_all_gather),
@@ -110,14 +111,19 @@ def _backend_classes() -> List[type]:
     return classes
 
 
-def patch_deepspeed(intra_node_pg_size: int, algorithm: Optional[str] = "auto") -> ProcessGroups:
+def patch_deepspeed(intra_node_pg_size: int, algorithm: Optional[str] = "auto",
+                    lanes: Optional[int] = None) -> ProcessGroups:
     """``algorithm``: "auto" (tuning table; default), or a fixed variant; ``None`` keeps the
-    reference's choice (recursive doubling / halving)."""
+    reference's choice (recursive doubling / halving).  ``lanes`` caps the number of SMs a
+    parameter gather or gradient reduction may occupy: inside a training step the collectives
+    overlap with GEMMs, and a few lanes that leave the other SMs to the math beat many lanes
+    that finish the transfer sooner."""
     assert dist.is_initialized()
     assert dist.get_world_size() % intra_node_pg_size == 0
     build_rank0_first(dist.barrier)
-    global pg, _algo
+    global pg, _algo, _lanes
     _algo = algorithm
+    _lanes = lanes
     if pg is None:
         pg = ProcessGroups(intra_node_pg_size, dist.get_world_size() // intra_node_pg_size)
     for cls in _backend_classes():

@@ -1,0 +1,73 @@
+"""tcgen05 GEMM and fused all-gather+GEMM against plain PyTorch fp32 references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rnd(shape, seed, scale=1.0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(shape, device=DEV, generator=g) * scale).to(torch.bfloat16)
+
+
+def check_close(y, ref, K):
+    # bf16 inputs, fp32 accumulation, one rounding to bf16 at the end
+    err = (y.float() - ref).abs().max()
+    tol = 2e-2 * ref.abs().max() + 1e-3
+    assert float(err) <= float(tol), f"max abs err {float(err):.4g} > {float(tol):.4g}"
+    rel = (y.float() - ref).norm() / ref.norm()
+    assert float(rel) < 5e-3, f"relative error {float(rel):.3e}"
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 128), (384, 768, 2048), (1000, 520, 328), (8192, 6144, 2048)])
+def test_gemm_matches_fp32_reference(shape):
+    import pccl
+
+    M, N, K = shape
+    A, W = rnd((M, K), 1), rnd((N, K), 2, 0.05)
+    bias = rnd((N,), 3)
+    y, err = pccl._C.gemm(A, W, bias, None)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    ref = A.float() @ W.float().t() + bias.float()
+    check_close(y, ref, K)
+    y2, err2 = pccl._C.gemm(A, W, None, None)
+    torch.cuda.synchronize()
+    assert int(err2.item()) == 0
+    check_close(y2, A.float() @ W.float().t(), K)
+
+
+def test_linear_wrapper_and_identity():
+    from pccl.ops.gemm import linear
+
+    K = 256
+    x = rnd((3, 50, K), 5)
+    eye = torch.eye(K, device=DEV, dtype=torch.bfloat16)
+    y = linear(x, eye, check=True)
+    assert torch.equal(y, x)                     # exact: one non-zero product per output
+    w = rnd((512, K), 6, 0.1)
+    y = linear(x, w, check=True)
+    check_close(y.view(-1, 512), x.view(-1, K).float() @ w.float().t(), K)
+    with pytest.raises(RuntimeError):
+        linear(rnd((4, 12), 1), rnd((8, 12), 2))   # K not a multiple of 8
+
+
+@pytest.mark.parametrize("P,me", [(2, 0), (4, 3), (8, 5)])
+def test_fused_gather_gemm_with_local_peers(P, me):
+    """The fused kernel with peers that are local buffers: gatherer CTAs pull every shard
+    into the local weight buffer while the GEMM CTAs multiply panel by panel."""
+    import pccl
+
+    M, K = 512, 512
+    N = P * 256 * 2
+    A = rnd((M, K), 11)
+    shards = [rnd((N // P, K), 20 + p, 0.05) for p in range(P)]
+    bias = rnd((N,), 40)
+    w_full = torch.zeros((N, K), device=DEV, dtype=torch.bfloat16)
+    y, err = pccl._C.ag_gemm_local(A, shards, me, w_full, bias, 4)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    W = torch.cat(shards)
+    assert torch.equal(w_full, W), "the gathered weight must be a bit-exact copy of the shards"
+    check_close(y, A.float() @ W.float().t() + bias.float(), K)
