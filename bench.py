@@ -49,6 +49,7 @@ def parse_args():
                     help="SMs a parameter gather / gradient reduction may occupy while it overlaps the GEMMs")
     ap.add_argument("--nvls", type=int, default=int(os.environ.get("PCCL_ENABLE_NVLS", "0")))
     ap.add_argument("--fused-ag-gemm", type=int, default=int(os.environ.get("PCCL_FUSED_AG_GEMM", "0")))
+    ap.add_argument("--gather-ctas", type=int, default=16)
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 
@@ -96,18 +97,14 @@ def main() -> None:
 
     comm = None
     if args.impl == "pccl":
-        heap = heap_bytes_needed(cfg, world) + (320 << 20)
+        heap = heap_bytes_needed(cfg, world, bool(args.fused_ag_gemm)) + (320 << 20)
         comm = pccl.init(heap_bytes=heap, staging_bytes=64 << 20, enable_nvls=bool(args.nvls))
         from pccl.patch_deepspeed import patch_deepspeed
 
         patch_deepspeed(world, algorithm=args.algorithm, lanes=args.lanes)
     backend = TorchBackend()
-    linear_fwd = None
-    if args.impl == "pccl" and args.fused_ag_gemm:
-        from pccl.ops.ag_gemm import make_linear_fwd
-
-        linear_fwd = make_linear_fwd(comm)
-    engine = Zero3Engine(cfg, backend, OptimConfig(), device=dev, comm=comm, linear_fwd=linear_fwd, micro_batch=mb)
+    engine = Zero3Engine(cfg, backend, OptimConfig(), device=dev, comm=comm, micro_batch=mb,
+                         fused_ag_gemm=(args.impl == "pccl" and bool(args.fused_ag_gemm)), gather_ctas=args.gather_ctas)
 
     total_steps = warmup + args.steps
     gen = torch.Generator(device="cpu").manual_seed(4321 + rank)
@@ -192,7 +189,7 @@ def main() -> None:
                 "global_batch": world * mb, "micro_batch_per_gpu": mb, "seq_len": S,
                 "parallelism": f"zero3-dp{world}", "optimizer": "AdamW fp32 master+moments, grad-norm clip 1.0",
                 "algorithm": args.algorithm, "lanes": args.lanes, "nvls": bool(args.nvls),
-                "fused_ag_gemm": bool(args.fused_ag_gemm),
+                "fused_ag_gemm": bool(engine.fused_ag_gemm),
                 "l2": "working set per step (tens of GB) exceeds the 126 MB L2; no explicit flush",
                 "transport": comm.transport_name if comm is not None else "nccl",
             },

@@ -118,9 +118,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
 struct TileSched {
   int tiles_m, tiles_n, total;
   int tiles_per_rank, P, me;   // fused mode: own panels first, then the peers' in arrival order
+  // Tiles are walked in bands of kGroupM row-tiles: the ~148 tiles in flight then cover a
+  // 16 x 9 patch of the output instead of 148 x 1, so one wave touches ~17 MB of A and W
+  // instead of ~80 MB and the operands are served from L2 rather than HBM.
+  // Fused mode walks all row-tiles of a panel before the next panel (group_m = tiles_m):
+  // panels are then needed as late as possible, in the order in which they arrive.
+  int group_m;
   __device__ __forceinline__ void decode(int t, int* m_idx, int* n_idx) const {
-    const int q = t / tiles_m;
-    *m_idx = t - q * tiles_m;
+    const int band_tiles = group_m * tiles_n;
+    const int band = t / band_tiles;
+    const int first_m = band * group_m;
+    const int rows = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
+    const int in_band = t - band * band_tiles;
+    const int q = in_band / rows;
+    *m_idx = first_m + in_band - q * rows;
     if (tiles_per_rank > 0) {
       const int r = (me + q / tiles_per_rank) % P;
       *n_idx = r * tiles_per_rank + q % tiles_per_rank;
@@ -129,6 +140,21 @@ struct TileSched {
     }
   }
 };
+
+// cp.async.bulk.wait_group takes an immediate: wait until at most n groups are pending.
+__device__ __forceinline__ void bulk_wait_pending(int n) {
+  switch (n) {
+    case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.bulk.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.bulk.wait_group 6;" ::: "memory"); break;
+    case 7: asm volatile("cp.async.bulk.wait_group 7;" ::: "memory"); break;
+    case 8: asm volatile("cp.async.bulk.wait_group 8;" ::: "memory"); break;
+    default: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;   // conservative
+  }
+}
 
 // ---------------------------------------------------------------- gatherer CTAs
 __device__ void gather_role(const GemmArgs& a, unsigned char* smem, int gi) {
@@ -143,38 +169,76 @@ __device__ void gather_role(const GemmArgs& a, unsigned char* smem, int gi) {
   const unsigned others = others_mask(P, me);
   char* w_full = reinterpret_cast<char*>(const_cast<void*>(a.W));
   if (flag_sync) cta_signal_mask(g, c, kSlotEntry, others);
-  unsigned entered = 0;
   bool ok = true;
-  // remote panels in the order in which the GEMM CTAs want them, dealt round-robin
-  const int nremote = (P - 1) * tpr;
-  for (int i = gi; i < nremote + tpr && ok; i += a.gather_ctas) {
-    // the last tpr entries are the own shard's panels (lowest priority: the GEMM reads them from the shard)
-    const int k = i < nremote ? 1 + i / tpr : 0;
-    const int j = i < nremote ? i % tpr : i - nremote;
-    const int p = (me + k) % P;
-    if (flag_sync && k != 0 && !((entered >> p) & 1u)) {
-      if (!cta_wait(g, c, kSlotEntry, p)) {
+  if (flag_sync && !cta_wait_mask(g, c, kSlotEntry, others)) ok = false;
+  // Every gatherer moves its slice of every panel as ONE continuous stream of 32 KiB chunks
+  // through the copy ring, panels in the order in which the GEMM CTAs want them (peers me+1,
+  // me+2, ..., the own shard last: the GEMM reads that from the shard itself).  A panel's
+  // flag is raised one panel later, when `wait_group` says that everything older than the
+  // newest panel's stores has been performed, so the pipeline never drains.
+  uint64_t lo, hi;
+  lane_range(panel_bytes, 16, gi, a.gather_ctas, &lo, &hi);
+  const uint64_t len = hi - lo;
+  if (threadIdx.x == 0 && ok && len > 0) {
+    const uint32_t cpp = (uint32_t)((len + kBulkStageBytes - 1) / kBulkStageBytes);   // chunks per panel slice
+    const uint32_t npanels = (uint32_t)(P * tpr);
+    const uint32_t total = npanels * cpp;
+    const int nremote = (P - 1) * tpr;
+    auto locate = [&](uint32_t ch, const char** src, char** dst, uint32_t* bytes, int* n_tile) {
+      const int i = (int)(ch / cpp);
+      const uint64_t off = (uint64_t)(ch % cpp) * kBulkStageBytes;
+      const int k = i < nremote ? 1 + i / tpr : 0;
+      const int j = i < nremote ? i % tpr : i - nremote;
+      const int p = (me + k) % P;
+      *n_tile = p * tpr + j;
+      *src = g.heap[p] + a.shard_off + (uint64_t)j * panel_bytes + lo + off;
+      *dst = w_full + (uint64_t)(*n_tile) * panel_bytes + lo + off;
+      *bytes = (uint32_t)((len - off) < kBulkStageBytes ? (len - off) : kBulkStageBytes);
+    };
+    auto issue = [&](uint32_t ch) {
+      const char* src; char* dst; uint32_t bytes; int nt;
+      locate(ch, &src, &dst, &bytes, &nt);
+      const uint32_t st = ch % kBulkStages;
+      mbar_expect_tx(pipe.full + st, bytes);
+      bulk_load(pipe.stages + (size_t)st * kBulkStageBytes, src, bytes, pipe.full + st);
+    };
+    auto raise = [&](int n_tile) {
+      asm volatile("fence.proxy.async;" ::: "memory");
+      __threadfence();
+      atomicAdd(a.panel_flags + n_tile, 1u);
+    };
+    asm volatile("fence.proxy.async;" ::: "memory");
+    uint32_t loaded = 0;
+    for (; loaded < total && loaded < (uint32_t)kBulkStages; ++loaded) issue(loaded);
+    int prev_tile = -1;
+    for (uint32_t ch = 0; ch < total; ++ch) {
+      const uint32_t st = ch % kBulkStages, parity = (ch / kBulkStages) & 1u;
+      if (!mbar_wait(pipe.full + st, parity, g.timeout_ns)) {
         ok = false;
         break;
       }
-      entered |= 1u << p;
+      const char* src; char* dst; uint32_t bytes; int nt;
+      locate(ch, &src, &dst, &bytes, &nt);
+      bulk_store(dst, pipe.stages + (size_t)st * kBulkStageBytes, bytes);
+      bulk_commit();
+      if (ch % cpp == cpp - 1) {            // the last chunk of a panel has been issued
+        if (prev_tile >= 0) {
+          bulk_wait_pending((int)cpp);      // everything older than this panel has landed
+          raise(prev_tile);
+        }
+        prev_tile = nt;
+      }
+      if (loaded < total) {
+        bulk_wait_read_all();
+        issue(loaded);
+        ++loaded;
+      }
     }
-    const int n_tile = p * tpr + j;
-    char* dst = w_full + (uint64_t)n_tile * panel_bytes;
-    const char* src = g.heap[p] + a.shard_off + (uint64_t)j * panel_bytes;
-    char* d[1] = {dst};
-    if (!cta_bulk_copy(pipe, d, 1, src, panel_bytes)) {
-      ok = false;
-      break;
-    }
-    cta_bulk_flush();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      atomicAdd(a.panel_flags + n_tile, 1u);
-    }
+    bulk_wait_all();
+    if (ok && prev_tile >= 0) raise(prev_tile);
+    if (!ok) atomicCAS(a.error, 0, kErrGather);
   }
-  if (!ok && threadIdx.x == 0) atomicCAS(a.error, 0, kErrGather);
+  __syncthreads();
   if (flag_sync) {
     cta_signal_mask(g, c, kSlotExit, others);   // I no longer read your shard
     cta_wait_mask(g, c, kSlotExit, others);     // nobody reads mine any more
@@ -230,6 +294,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   sch.P = a.g.size;
   sch.me = a.g.first_local;
   sch.tiles_per_rank = a.gather_ctas > 0 ? (a.N / sch.P) / BN : 0;
+  sch.group_m = a.gather_ctas > 0 ? sch.tiles_m : (sch.tiles_m < 16 ? sch.tiles_m : 16);
   const int nkb = (a.K + BK - 1) / BK;
 
   if (warp == 0 && lane == 0) {
@@ -254,7 +319,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (;;) {
             uint32_t v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            if (v != 0) break;
+            if (v >= (uint32_t)a.gather_ctas) break;
             if ((++spins & 63u) == 0u) {
               if (*abort_flag != 0 || global_timer_ns() - t0 > kWaitNs) {
                 ok = false;

@@ -39,6 +39,37 @@ def _wait(handle) -> None:
         handle.wait()
 
 
+class _Handles:
+    """Several asynchronous collectives that are waited for together."""
+
+    def __init__(self, handles):
+        self.handles = [h for h in handles if h is not None]
+
+    def wait(self) -> None:
+        for h in self.handles:
+            h.wait()
+
+
+def unit_regions(unit: gpt.UnitSpec, world: int, fused: bool):
+    """Cut a unit's flat parameter space into regions that are sharded separately.
+
+    Normally a unit is one region, split evenly over the ranks.  With the fused
+    all-gather+GEMM the QKV and FC1 weights are regions of their own, sharded by ROWS, so
+    that the fused kernel can gather exactly one weight; everything else is the third
+    region.  Returns [(offset, length)] in the gathered layout; lengths are multiples of
+    256 * world."""
+    gran = world * 256
+    pad = lambda n: (n + gran - 1) // gran * gran  # noqa: E731
+    names = {p.name: p for p in unit.params}
+    if not fused or "qkv_w" not in names:
+        return [(0, pad(unit.numel))]
+    qkv, fc1 = names["qkv_w"], names["fc1_w"]
+    assert qkv.offset == 0 and fc1.offset == qkv.numel, "fused layout expects qkv_w then fc1_w at the front of the unit"
+    assert qkv.numel % gran == 0 and fc1.numel % gran == 0
+    rest = fc1.offset + fc1.numel
+    return [(0, qkv.numel), (fc1.offset, fc1.numel), (rest, pad(unit.numel - rest))]
+
+
 @dataclass
 class OptimConfig:
     lr: float = 1e-4
@@ -49,12 +80,11 @@ class OptimConfig:
     max_grad_norm: float = 1.0
 
 
-def heap_bytes_needed(cfg: GPTConfig, world: int) -> int:
+def heap_bytes_needed(cfg: GPTConfig, world: int, fused: bool = False) -> int:
     """Symmetric-heap bytes the engine allocates for ``cfg`` on ``world`` ranks (without
     the communicator's staging area)."""
     units = gpt.unit_specs(cfg)
-    gran = world * 256
-    padded = [(u.numel + gran - 1) // gran * gran for u in units]
+    padded = [sum(r[1] for r in unit_regions(u, world, fused)) for u in units]
     total_shard = sum(n // world for n in padded)
     max_layer = max(padded[1:]) if len(padded) > 1 else padded[0]
     elems = total_shard + 2 * max(padded) + 2 * max_layer + padded[0]
@@ -64,7 +94,8 @@ def heap_bytes_needed(cfg: GPTConfig, world: int) -> int:
 class Zero3Engine:
     def __init__(self, cfg: GPTConfig, backend: Optional[TorchBackend] = None, optim: Optional[OptimConfig] = None,
                  device: Optional[torch.device] = None, seed: int = 1234, comm=None, group=None,
-                 linear_fwd: Optional[Callable] = None, micro_batch: int = 1):
+                 linear_fwd: Optional[Callable] = None, micro_batch: int = 1, fused_ag_gemm: bool = False,
+                 gather_ctas: int = 16):
         from .. import build_kernels
 
         self.C = build_kernels.load()
@@ -82,9 +113,23 @@ class Zero3Engine:
         self.launches = 0          # kernels of this library launched by the last step
         self.units = gpt.unit_specs(cfg)
         P = self.world
-        gran = P * 256
-        self.padded = [(u.numel + gran - 1) // gran * gran for u in self.units]
-        self.shard_len = [n // P for n in self.padded]
+        # the fused kernel wants every rank to own whole 256-row panels of the QKV and FC1 weights
+        rows_ok = (3 * cfg.d_model) % (P * 256) == 0 and cfg.d_ff % (P * 256) == 0 and cfg.d_model % 8 == 0
+        self.fused_ag_gemm = bool(fused_ag_gemm) and rows_ok and P > 1 and comm is not None and \
+            comm.native is not None and bool(getattr(self.backend, "symmetric_memory", False))
+        self.gather_ctas = gather_ctas
+        # regions[ui] = [(offset, length)] in the gathered layout; a unit's shard is the
+        # concatenation of its regions' shards
+        self.regions = [unit_regions(u, P, self.fused_ag_gemm) for u in self.units]
+        self.padded = [rg[-1][0] + rg[-1][1] for rg in self.regions]
+        self.shard_len = [sum(l for _o, l in rg) // P for rg in self.regions]
+        self.region_shard_off = []       # offset of each region's shard inside the unit's shard
+        for rg in self.regions:
+            offs, acc = [], 0
+            for _o, l in rg:
+                offs.append(acc)
+                acc += l // P
+            self.region_shard_off.append(offs)
         self.shard_off = [0]
         for n in self.shard_len:
             self.shard_off.append(self.shard_off[-1] + n)
@@ -119,6 +164,14 @@ class Zero3Engine:
         self.gviews = [None] + [[gpt.views(u, buf) for buf in self.gradbuf] for u in self.units[1:]]
         self.gviews0 = gpt.views(self.units[0], self.gradbuf0)
         self.main = torch.cuda.current_stream(self.device)
+        self._cur = None
+        self._gemm_errs: List[torch.Tensor] = []
+        self._fused_gid = None
+        if self.fused_ag_gemm:
+            from ..patch_deepspeed import get_heir_pg
+
+            self._fused_gid = get_heir_pg().get_flat_group().gid
+            self.linear_fwd = self._fused_linear
         self._rs_pending: List = [None, None]
         self._tokens_dev: Optional[torch.Tensor] = None
         self._targets_dev: Optional[torch.Tensor] = None
@@ -129,27 +182,57 @@ class Zero3Engine:
         for ui, u in enumerate(self.units):
             full = torch.empty(self.padded[ui], dtype=torch.float32, device=self.device)
             gpt.init_unit(u, full, self.cfg, seed + ui)
-            mine = full.view(P, -1)[r]
-            sl = slice(self.shard_off[ui], self.shard_off[ui + 1])
-            self.master[sl].copy_(mine)
-            self.param_shard[sl].copy_(mine)
+            for (g_off, g_len), s_off in zip(self.regions[ui], self.region_shard_off[ui]):
+                mine = full[g_off:g_off + g_len].view(P, -1)[r]
+                lo = self.shard_off[ui] + s_off
+                self.master[lo:lo + g_len // P].copy_(mine)
+                self.param_shard[lo:lo + g_len // P].copy_(mine)
             del full
         torch.cuda.synchronize(self.device)
 
     # ------------------------------------------------------------------ communication
-    def _gather(self, ui: int, slot: int):
-        """Start the all-gather of unit ``ui`` into rotating buffer ``slot``."""
-        out = self.gathered[slot][: self.padded[ui]]
-        inp = self.param_shard[self.shard_off[ui]: self.shard_off[ui + 1]]
-        return self.backend.all_gather_into_tensor(out, inp, group=self.group, async_op=True)
+    def _region_shard(self, buf: torch.Tensor, ui: int, ri: int) -> torch.Tensor:
+        lo = self.shard_off[ui] + self.region_shard_off[ui][ri]
+        return buf[lo: lo + self.regions[ui][ri][1] // self.world]
+
+    def _gather(self, ui: int, slot: int, skip=()):
+        """Start the all-gather of unit ``ui`` into rotating buffer ``slot`` (one collective per
+        region; ``skip`` names regions that a fused all-gather+GEMM will fetch itself)."""
+        hs = []
+        for ri, (g_off, g_len) in enumerate(self.regions[ui]):
+            if ri in skip:
+                continue
+            out = self.gathered[slot][g_off: g_off + g_len]
+            hs.append(self.backend.all_gather_into_tensor(out, self._region_shard(self.param_shard, ui, ri),
+                                                          group=self.group, async_op=True))
+        return hs[0] if len(hs) == 1 else _Handles(hs)
 
     def _reduce(self, ui: int, buf: torch.Tensor):
         """Start the reduce-scatter of unit ``ui``'s gradient buffer into the gradient shard."""
-        inp = buf[: self.padded[ui]]
-        out = self.grad_shard[self.shard_off[ui]: self.shard_off[ui + 1]]
-        if self.fused_scale:
-            return self.backend.reduce_scatter_tensor(out, inp, group=self.group, async_op=True, scale=1.0 / self.world)
-        return self.backend.reduce_scatter_tensor(out, inp, group=self.group, async_op=True)
+        hs = []
+        for ri, (g_off, g_len) in enumerate(self.regions[ui]):
+            inp = buf[g_off: g_off + g_len]
+            out = self._region_shard(self.grad_shard, ui, ri)
+            if self.fused_scale:
+                hs.append(self.backend.reduce_scatter_tensor(out, inp, group=self.group, async_op=True,
+                                                             scale=1.0 / self.world))
+            else:
+                hs.append(self.backend.reduce_scatter_tensor(out, inp, group=self.group, async_op=True))
+        return hs[0] if len(hs) == 1 else _Handles(hs)
+
+    def _fused_linear(self, x, w, b, which):
+        """Forward hook for QKV / FC1 of the layer being computed: ONE kernel gathers the
+        weight's row shards over NVLink into its place in the gathered buffer and multiplies."""
+        if which not in ("qkv", "fc1") or self._cur is None:
+            return torch.nn.functional.linear(x, w, b)
+        li, slot = self._cur
+        ri = 0 if which == "qkv" else 1
+        n_rows, k = w.shape
+        shard = self._region_shard(self.param_shard, li, ri).view(n_rows // self.world, k)
+        gid = self._fused_gid
+        y, err = self.C.ag_gemm(self.comm.native, gid, x, shard, w, b, None, self.gather_ctas)
+        self._gemm_errs.append(err)
+        return y
 
     # ------------------------------------------------------------------ one training step
     @torch.no_grad()
@@ -177,7 +260,7 @@ class Zero3Engine:
         # ---- forward
         stage = 0
         pending = self._gather(0, 0)
-        nxt = self._gather(1, 1) if L > 0 else None
+        nxt = self._gather(1, 1, (0, 1) if self.fused_ag_gemm else ()) if L > 0 else None
         _wait(pending)
         x = gpt.embed_forward(tokens, self.pviews[0][0])
         saved = []
@@ -186,8 +269,11 @@ class Zero3Engine:
             _wait(nxt)
             # the buffer that the next prefetch overwrites was last read by the previous stage,
             # which is already queued on this stream; the async launch orders itself after it
-            nxt = self._gather(li + 1, 1 - slot) if li < L else self._gather(0, 1 - slot)
+            skip = (0, 1) if self.fused_ag_gemm else ()
+            nxt = self._gather(li + 1, 1 - slot, skip) if li < L else self._gather(0, 1 - slot)
+            self._cur = (li, slot)
             x, ctx = gpt.layer_forward(x, self.pviews[li][slot], cfg, B, self.linear_fwd)
+            self._cur = None
             saved.append(ctx)
         # ---- head: final norm, tied projection, loss; forward and backward together
         head_slot = (L + 1) % 2
@@ -221,8 +307,15 @@ class Zero3Engine:
                 o.eps, o.weight_decay, self.step_count, 1.0, o.max_grad_norm,
                 self.sq_norm if o.max_grad_norm > 0 else None)
         own = 2 + (1 if o.max_grad_norm > 0 else 0) + (T + 4095) // 4096
+        self._gemm_errs.clear()
         self.launches = own + (self._native_launches() - launches0)
         return self.loss_sum / T
+
+    def check_errors(self) -> None:
+        """Synchronise and raise if a kernel of the last steps gave up in a bounded wait."""
+        torch.cuda.synchronize(self.device)
+        if self.comm is not None:
+            self.comm.check(sync=False)
 
     def _ce(self, logits, targets, loss_sum, grad_scale) -> None:
         self.C.ce_fwd_bwd(logits, targets, loss_sum, grad_scale, -100)

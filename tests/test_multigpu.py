@@ -107,6 +107,43 @@ def test_zero3_training_matches_nccl_engine(port):
     run_ranks(_zero3, _world(), port, backend="nccl", timeout=120)
 
 
+def _zero3_fused(rank, world):
+    """The engine with the fused all-gather+GEMM on QKV and FC1 (row-sharded weights) trains
+    like the NCCL-backed engine."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import pccl
+    from pccl.models.gpt import GPTConfig
+    from pccl.parallel.backend import TorchBackend
+    from pccl.parallel.zero3 import OptimConfig, Zero3Engine, heap_bytes_needed
+    from pccl.patch_deepspeed import patch_deepspeed, unpatch_deepspeed
+
+    dev = torch.device("cuda", rank)
+    d = 256 * world                      # every rank owns whole 256-row panels of QKV and FC1
+    cfg = GPTConfig(2, d, d // 64, 4 * d, vocab=1024, seq_len=128, name="gpt-fused-test")
+    gen = torch.Generator().manual_seed(19 + rank)
+    toks = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=gen).to(dev)
+    base = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=1e-3), device=dev)
+    l_base = [float(base.train_step(toks[:, :-1], toks[:, 1:])) for _ in range(3)]
+    del base
+    comm = pccl.init(heap_bytes=heap_bytes_needed(cfg, world, True) + (128 << 20), staging_bytes=32 << 20,
+                     enable_nvls=False, timeout_ms=5000)
+    patch_deepspeed(world)
+    ours = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=1e-3), device=dev, comm=comm, fused_ag_gemm=True,
+                       gather_ctas=8)
+    assert ours.fused_ag_gemm and len(ours.regions[1]) == 3
+    l_ours = [float(ours.train_step(toks[:, :-1], toks[:, 1:])) for _ in range(3)]
+    ours.check_errors()
+    unpatch_deepspeed()
+    for a, b in zip(l_base, l_ours):
+        assert abs(a - b) < 3e-2, (l_base, l_ours)
+    dist.barrier()
+    pccl.shutdown()
+
+
+def test_zero3_with_fused_all_gather_gemm(port):
+    run_ranks(_zero3_fused, _world(), port, backend="nccl", timeout=120)
+
+
 def _leaver(rank, world):
     """A rank leaves between steps; the others learn of it from their bounded waits (a
     short timeout), get an exception, and their CUDA context keeps working."""
