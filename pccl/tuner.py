@@ -23,7 +23,7 @@ TABLE_PATH = Path(__file__).resolve().parent / "tuning_table.json"
 
 # Fallback when the table has no row: bytes each lane should at least move, lane ceiling.
 MIN_BYTES_PER_LANE = 128 << 10
-DEFAULT_MAX_LANES = 64
+DEFAULT_MAX_LANES = 148
 
 
 @lru_cache(maxsize=1)
@@ -45,12 +45,30 @@ def default_lanes(nbytes: int, max_lanes: int = DEFAULT_MAX_LANES) -> int:
     return int(lanes)
 
 
-def lookup(collective: str, world: int, nbytes: int) -> Optional[Tuple[str, int]]:
+def lookup(collective: str, world: int, nbytes: int) -> Optional[Tuple[List[str], int]]:
+    """Row of the table for this size: (variants in order of preference, lanes)."""
     rows: List = _table().get(collective, {}).get(str(world), [])
-    for max_bytes, algo, lanes in rows:
+    for max_bytes, algos, lanes in rows:
         if max_bytes is None or nbytes <= max_bytes:
-            return algo, int(lanes)
+            return ([algos] if isinstance(algos, str) else list(algos)), int(lanes)
     return None
+
+
+def _feasible(collective: str, algo: str, world: int, nbytes: int, symmetric_in: bool, symmetric_out: bool,
+              has_multimem: bool) -> bool:
+    """Variants that read or multicast peer memory need the right tensors in the heap."""
+    if algo == sch.MULTIMEM:
+        if not has_multimem or nbytes % 16 != 0:
+            return False
+        if collective == "all_gather" and not symmetric_out:
+            return False
+        if collective in ("reduce_scatter", "all_reduce") and not symmetric_in:
+            return False
+    if collective == "reduce_scatter" and algo == sch.PULL and not symmetric_in:
+        return False
+    if algo == sch.RECURSIVE and not sch.is_pow2(world):
+        return False
+    return True
 
 
 def choose(collective: str, world: int, nbytes: int, *, requested: str = sch.AUTO, symmetric_in: bool = False,
@@ -65,21 +83,16 @@ def choose(collective: str, world: int, nbytes: int, *, requested: str = sch.AUT
     picked_lanes = None
     if algo == sch.AUTO:
         hit = lookup(collective, world, nbytes)
-        if hit is not None:
-            algo, picked_lanes = hit
-        else:
-            algo = sch.DIRECT
-    # Variants that read or multicast peer memory need the right tensors in the heap.
-    if algo == sch.MULTIMEM and not has_multimem:
+        candidates, picked_lanes = hit if hit is not None else ([sch.DIRECT], None)
         algo = sch.DIRECT
-    if collective == "reduce_scatter" and algo in (sch.PULL, sch.MULTIMEM) and not symmetric_in:
-        algo = sch.DIRECT
-    if collective == "all_gather" and algo == sch.MULTIMEM and (nbytes % 16 != 0):
-        algo = sch.DIRECT
-    if algo == sch.RECURSIVE and not sch.is_pow2(world):
-        if requested == sch.RECURSIVE:
+        for cand in candidates:
+            if _feasible(collective, cand, world, nbytes, symmetric_in, symmetric_out, has_multimem):
+                algo = cand
+                break
+    elif not _feasible(collective, algo, world, nbytes, symmetric_in, symmetric_out, has_multimem):
+        if algo == sch.RECURSIVE and requested == sch.RECURSIVE:
             sch.check_algo(algo, world)   # raises: the caller asked for it explicitly
         algo = sch.DIRECT
     if lanes is None:
-        lanes = int(env_lanes) if env_lanes else (picked_lanes or default_lanes(nbytes, max_lanes))
+        lanes = int(env_lanes) if env_lanes else min(picked_lanes or 64, default_lanes(nbytes, max_lanes))
     return algo, max(1, min(int(lanes), max_lanes))
