@@ -87,6 +87,13 @@ void all_gather(Comm& c, int gid, std::vector<at::Tensor> outs, std::vector<at::
   const uint64_t n = (uint64_t)ins[0].nbytes();
   if (n == 0) return;
   cudaStream_t stream = current_stream(dev);
+  if (P == 1) {
+    // A group of one: the gather is a device-to-device copy, which the copy engine does
+    // without occupying an SM.
+    if (outs[0].data_ptr() != ins[0].data_ptr())
+      PCCL_CUDA(cudaMemcpyAsync(outs[0].data_ptr(), ins[0].data_ptr(), n, cudaMemcpyDeviceToDevice, stream));
+    return;
+  }
   const int64_t out_off = symmetric_offset(c, gid, l, outs);
   const int64_t in_off = symmetric_offset(c, gid, l, ins);
 
