@@ -41,6 +41,7 @@ SOURCES = [
     "collectives.cu",
     "gemm_sm100.cu",
     "optim.cu",
+    "train_ops.cu",
     "noalloc.cu",
 ]
 

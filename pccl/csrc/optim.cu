@@ -41,14 +41,48 @@ __device__ __forceinline__ float block_reduce(float v, float* smem) {
 }
 
 // ---------------------------------------------------------------- squared norm
-// Grid-stride partial sums, one atomicAdd per block into *out (zeroed by the caller).
+// Grid-stride partial sums over 16-byte vectors (four in flight per thread), one atomicAdd per
+// block into *out (zeroed by the caller).
+template <typename T>
+__device__ __forceinline__ float sq8(const uint4& q);
+template <>
+__device__ __forceinline__ float sq8<__nv_bfloat16>(const uint4& q) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  float a = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xffff0000u);
+    a += lo * lo + hi * hi;
+  }
+  return a;
+}
+template <>
+__device__ __forceinline__ float sq8<float>(const uint4& q) {
+  const float a = __uint_as_float(q.x), b = __uint_as_float(q.y), c = __uint_as_float(q.z), d = __uint_as_float(q.w);
+  return a * a + b * b + c * c + d * d;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kOptThreads) sq_norm_kernel(const T* __restrict__ x, uint64_t n, float* out) {
   __shared__ float red[32];
+  constexpr uint64_t EPV = 16 / sizeof(T);
   float acc = 0.f;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
-    const float v = (float)x[i];
-    acc += v * v;
+  uint64_t done = 0;
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+    const uint64_t nvec = n / EPV;
+    const uint4* v = reinterpret_cast<const uint4*>(x);
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      const uint4 a = v[i], b = v[i + stride], c = v[i + 2 * stride], d = v[i + 3 * stride];
+      acc += sq8<T>(a) + sq8<T>(b) + sq8<T>(c) + sq8<T>(d);
+    }
+    for (; i < nvec; i += stride) acc += sq8<T>(v[i]);
+    done = nvec * EPV;
+  }
+  for (uint64_t i = done + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    const float f = (float)x[i];
+    acc += f * f;
   }
   acc = block_reduce<false>(acc, red);
   if (threadIdx.x == 0) atomicAdd(out, acc);

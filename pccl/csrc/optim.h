@@ -22,4 +22,16 @@ cudaError_t launch_adamw(float* master, float* m, float* v, const void* grad, in
 cudaError_t launch_ce_fwd_bwd(void* logits_bf16, const int64_t* targets, float* loss_sum, int64_t rows, int vocab,
                               int64_t row_stride, float grad_scale, int64_t ignore_index, cudaStream_t s);
 
+// out[c] = sum over rows of X[T, N] (bf16, N % 8 == 0).  partial: R*N floats, counters: ceil(N/64)
+// ints that are zero on entry and zero again on exit.
+int col_sum_row_splits(int64_t T, int N);
+cudaError_t launch_col_sum(const void* X, int64_t T, int N, void* out, float* partial, int* counters, int R,
+                           cudaStream_t s);
+
+// Layer-norm backward for bf16 activations with d in {1024, 2048, 4096}: writes dx, dgamma, dbeta.
+// pgamma / pbeta: 2 * ln_bwd_blocks() * d floats of scratch each.
+int ln_bwd_blocks();
+cudaError_t launch_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma, void* dx,
+                          void* dgamma, void* dbeta, float* pgamma, float* pbeta, int64_t T, int d, cudaStream_t s);
+
 }  // namespace pccl

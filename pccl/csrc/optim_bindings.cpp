@@ -74,9 +74,71 @@ void ce_fwd_bwd(at::Tensor& logits, const at::Tensor& targets, at::Tensor& loss_
                               at::cuda::getCurrentCUDAStream().stream()));
 }
 
+// Scratch that lives as long as the process: one buffer per device, grown on demand.
+at::Tensor& scratch(int device, int64_t floats) {
+  static at::Tensor bufs[64];
+  at::Tensor& b = bufs[device & 63];
+  if (!b.defined() || b.numel() < floats)
+    b = at::zeros({std::max<int64_t>(floats, 1 << 20)}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device));
+  return b;
+}
+at::Tensor& counters(int device, int64_t ints) {
+  static at::Tensor bufs[64];
+  at::Tensor& b = bufs[device & 63];
+  if (!b.defined() || b.numel() < ints)
+    b = at::zeros({std::max<int64_t>(ints, 4096)}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  return b;
+}
+
+void col_sum(const at::Tensor& x, at::Tensor& out) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous(),
+              "x must be a contiguous 2-D bfloat16 CUDA tensor");
+  check_flat(out, "out", at::kBFloat16);
+  const int64_t T = x.size(0);
+  const int N = (int)x.size(1);
+  TORCH_CHECK(out.numel() == N && N % 8 == 0 && ((uintptr_t)x.data_ptr()) % 16 == 0, "out must hold N elements, N % 8 == 0");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int dev = x.get_device();
+  const int R = col_sum_row_splits(T, N);
+  at::Tensor& part = scratch(dev, (int64_t)R * N);
+  at::Tensor& cnt = counters(dev, (N + 63) / 64);
+  PCCL_CUDA(launch_col_sum(x.data_ptr(), T, N, out.data_ptr(), part.data_ptr<float>(), cnt.data_ptr<int>(), R,
+                           at::cuda::getCurrentCUDAStream().stream()));
+}
+
+bool ln_bwd_supported(int64_t d) { return d == 1024 || d == 2048 || d == 4096; }
+
+at::Tensor ln_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& mean, const at::Tensor& rstd,
+                  const at::Tensor& gamma, at::Tensor& dgamma, at::Tensor& dbeta) {
+  TORCH_CHECK(dy.is_cuda() && dy.dim() == 2 && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous(), "dy: 2-D bf16");
+  TORCH_CHECK(x.sizes() == dy.sizes() && x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "x must match dy");
+  const int64_t T = dy.size(0), d = dy.size(1);
+  TORCH_CHECK(ln_bwd_supported(d), "layer-norm backward kernel takes d in {1024, 2048, 4096}");
+  check_flat(mean, "mean", at::kFloat);
+  check_flat(rstd, "rstd", at::kFloat);
+  check_flat(gamma, "gamma", at::kBFloat16);
+  check_flat(dgamma, "dgamma", at::kBFloat16);
+  check_flat(dbeta, "dbeta", at::kBFloat16);
+  TORCH_CHECK(mean.numel() == T && rstd.numel() == T && gamma.numel() == d && dgamma.numel() == d && dbeta.numel() == d,
+              "size mismatch");
+  c10::cuda::CUDAGuard guard(dy.device());
+  const int dev = dy.get_device();
+  at::Tensor dx = at::empty_like(dy);
+  const int64_t part = (int64_t)2 * ln_bwd_blocks() * d;
+  at::Tensor& sc = scratch(dev, 2 * part + (int64_t)64 * 8192);
+  float* pg = sc.data_ptr<float>() + (int64_t)64 * 8192;     // the front of the buffer belongs to col_sum
+  PCCL_CUDA(launch_ln_bwd(dy.data_ptr(), x.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr(),
+                          dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), pg, pg + part, T, (int)d,
+                          at::cuda::getCurrentCUDAStream().stream()));
+  return dx;
+}
+
 }  // namespace
 
 void bind_optim(py::module_& m) {
+  m.def("col_sum", &col_sum, "out[c] = sum_r x[r, c] (bf16 in/out, fp32 accumulation)");
+  m.def("ln_bwd", &ln_bwd, "layer-norm backward: returns dx, writes dgamma and dbeta");
+  m.def("ln_bwd_supported", &ln_bwd_supported);
   m.def("sq_norm", &sq_norm, "out += sum(x*x)");
   m.def("adamw", &adamw, py::arg("master"), py::arg("exp_avg"), py::arg("exp_avg_sq"), py::arg("grad"), py::arg("param"),
         py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"),

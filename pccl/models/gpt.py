@@ -149,7 +149,33 @@ def _ln_fwd(x, w, b, eps):
     return torch.ops.aten.native_layer_norm(x, [x.shape[-1]], w, b, eps)
 
 
+_native = None
+native_launches = 0     # kernels of this library launched by the functions below (col_sum, ln_bwd + finalize)
+
+
+def _kernels():
+    """The native extension, or False where it cannot be loaded (pure-PyTorch fallback)."""
+    global _native
+    if _native is None:
+        try:
+            from .. import build_kernels
+
+            _native = build_kernels.load()
+        except Exception:  # noqa: BLE001
+            _native = False
+    return _native
+
+
+def _fast(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.is_contiguous() and bool(_kernels())
+
+
 def _ln_bwd(dy, x, mean, rstd, w, b, gw, gb):
+    if _fast(dy) and _fast(x) and x.shape[-1] in (1024, 2048, 4096) and gw.is_contiguous() and gb.is_contiguous():
+        # one pass over dy and x: dx plus the weight/bias gradients, written in place
+        global native_launches
+        native_launches += 2
+        return _kernels().ln_bwd(dy, x, mean.view(-1), rstd.view(-1), w, gw, gb)
     dx, dw, db = torch.ops.aten.native_layer_norm_backward(dy, x, [x.shape[-1]], mean, rstd, w, b, [True, True, True])
     gw.copy_(dw)
     gb.copy_(db)
@@ -159,7 +185,12 @@ def _ln_bwd(dy, x, mean, rstd, w, b, gw, gb):
 def _wgrad(dy: torch.Tensor, x: torch.Tensor, gw: torch.Tensor, gb: Optional[torch.Tensor]) -> None:
     torch.mm(dy.t(), x, out=gw)
     if gb is not None:
-        torch.sum(dy, dim=0, out=gb)
+        if _fast(dy) and dy.shape[1] % 8 == 0 and gb.is_contiguous():
+            global native_launches
+            native_launches += 1
+            _kernels().col_sum(dy, gb)
+        else:
+            torch.sum(dy, dim=0, out=gb)
 
 
 def layer_forward(x: torch.Tensor, p: Dict[str, torch.Tensor], cfg: GPTConfig, batch: int,
@@ -201,11 +232,9 @@ def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[s
     da = torch.mm(dx2, p["proj_w"])
     datt = da.view(batch, S, H, dh).transpose(1, 2)
     dq, dk, dv = torch.autograd.grad(att, (qd, kd, vd), datt)
-    dqkv = torch.empty(batch, S, 3, H, dh, dtype=x.dtype, device=x.device)
-    dqkv[:, :, 0].copy_(dq.transpose(1, 2))
-    dqkv[:, :, 1].copy_(dk.transpose(1, 2))
-    dqkv[:, :, 2].copy_(dv.transpose(1, 2))
-    dqkv = dqkv.view(T, 3 * d)
+    # the attention backward returns its gradients in the memory order of q, k, v ([B, S, H, dh]
+    # underneath), so the [T, d] forms are views and one concatenation packs them as [T, 3d]
+    dqkv = torch.cat([t.transpose(1, 2).reshape(T, d) for t in (dq, dk, dv)], dim=1)
     _wgrad(dqkv, h1, gr["qkv_w"], gr["qkv_b"])
     dh1 = torch.mm(dqkv, p["qkv_w"])
     dx = _ln_bwd(dh1, x, mean1, rstd1, p["ln1_w"], p["ln1_b"], gr["ln1_w"], gr["ln1_b"]).add_(dx2)

@@ -145,14 +145,20 @@ class Zero3Engine:
             return torch.empty(n, dtype=torch.bfloat16, device=self.device)
 
         self.param_shard = alloc(total_shard)
-        self.gathered = [alloc(max_unit), alloc(max_unit)]
-        self.gradbuf = [alloc(max_layer), alloc(max_layer)]
-        self.gradbuf0 = alloc(self.padded[0])
-        for b in self.gradbuf + [self.gradbuf0]:
-            b.zero_()
-        self.fused_scale = bool(getattr(self.backend, "fused_scale", False))
+        # One rank owns everything: the "gathered" parameters are the shard itself and the
+        # gradient buffers are the gradient shard, so there is nothing to gather or reduce.
+        self.local_only = P == 1
+        self.fused_scale = bool(getattr(self.backend, "fused_scale", False)) and not self.local_only
         gdt = torch.float32 if self.fused_scale else torch.bfloat16
         self.grad_shard = torch.zeros(total_shard, dtype=gdt, device=self.device)
+        if self.local_only:
+            self.gathered, self.gradbuf, self.gradbuf0 = [], [], None
+        else:
+            self.gathered = [alloc(max_unit), alloc(max_unit)]
+            self.gradbuf = [alloc(max_layer), alloc(max_layer)]
+            self.gradbuf0 = alloc(self.padded[0])
+            for b in self.gradbuf + [self.gradbuf0]:
+                b.zero_()
         self.master = torch.empty(total_shard, dtype=torch.float32, device=self.device)
         self.exp_avg = torch.zeros(total_shard, dtype=torch.float32, device=self.device)
         self.exp_avg_sq = torch.zeros(total_shard, dtype=torch.float32, device=self.device)
@@ -160,9 +166,18 @@ class Zero3Engine:
         self.loss_sum = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._init_params(seed)
         # views of every unit in each rotating buffer
-        self.pviews = [[gpt.views(u, buf) for buf in self.gathered] for u in self.units]
-        self.gviews = [None] + [[gpt.views(u, buf) for buf in self.gradbuf] for u in self.units[1:]]
-        self.gviews0 = gpt.views(self.units[0], self.gradbuf0)
+        if self.local_only:
+            def unit_of(buf, ui):
+                return buf[self.shard_off[ui]: self.shard_off[ui + 1]]
+
+            self.pviews = [[gpt.views(u, unit_of(self.param_shard, ui))] * 2 for ui, u in enumerate(self.units)]
+            self.gviews = [None] + [[gpt.views(u, unit_of(self.grad_shard, ui))] * 2
+                                    for ui, u in enumerate(self.units) if ui > 0]
+            self.gviews0 = gpt.views(self.units[0], unit_of(self.grad_shard, 0))
+        else:
+            self.pviews = [[gpt.views(u, buf) for buf in self.gathered] for u in self.units]
+            self.gviews = [None] + [[gpt.views(u, buf) for buf in self.gradbuf] for u in self.units[1:]]
+            self.gviews0 = gpt.views(self.units[0], self.gradbuf0)
         self.main = torch.cuda.current_stream(self.device)
         self._cur = None
         self._gemm_errs: List[torch.Tensor] = []
@@ -198,6 +213,8 @@ class Zero3Engine:
     def _gather(self, ui: int, slot: int, skip=()):
         """Start the all-gather of unit ``ui`` into rotating buffer ``slot`` (one collective per
         region; ``skip`` names regions that a fused all-gather+GEMM will fetch itself)."""
+        if self.local_only:
+            return None
         hs = []
         for ri, (g_off, g_len) in enumerate(self.regions[ui]):
             if ri in skip:
@@ -209,6 +226,8 @@ class Zero3Engine:
 
     def _reduce(self, ui: int, buf: torch.Tensor):
         """Start the reduce-scatter of unit ``ui``'s gradient buffer into the gradient shard."""
+        if self.local_only:
+            return None
         hs = []
         for ri, (g_off, g_len) in enumerate(self.regions[ui]):
             inp = buf[g_off: g_off + g_len]
@@ -251,7 +270,7 @@ class Zero3Engine:
         B, S = tokens.shape
         T = B * S
         L = cfg.n_layer
-        launches0 = self._native_launches()
+        launches0 = self._native_launches() + gpt.native_launches
         self.loss_sum.zero_()
         self.sq_norm.zero_()
         # without a fused scale in the reduce-scatter the 1/P of the average rides on the loss gradient
@@ -289,7 +308,7 @@ class Zero3Engine:
             gslot = li % 2
             _wait(self._rs_pending[gslot])          # the buffer's previous reduce-scatter has read it
             dx = gpt.layer_backward(dx, saved.pop(), self.pviews[li][slot], self.gviews[li][gslot], cfg, B)
-            self._rs_pending[gslot] = self._reduce(li, self.gradbuf[gslot])
+            self._rs_pending[gslot] = self._reduce(li, None if self.local_only else self.gradbuf[gslot])
         gpt.embed_backward(dx, tokens, self.gviews0)
         rs0 = self._reduce(0, self.gradbuf0)
         for h in self._rs_pending + [rs0]:
@@ -308,7 +327,7 @@ class Zero3Engine:
                 self.sq_norm if o.max_grad_norm > 0 else None)
         own = 2 + (1 if o.max_grad_norm > 0 else 0) + (T + 4095) // 4096
         self._gemm_errs.clear()
-        self.launches = own + (self._native_launches() - launches0)
+        self.launches = own + (self._native_launches() + gpt.native_launches - launches0)
         return self.loss_sum / T
 
     def check_errors(self) -> None:
