@@ -124,7 +124,7 @@ def main() -> None:
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
-    sampler = ClockSampler(torch.cuda.current_device()).start()
+    sampler = ClockSampler(torch.cuda.current_device(), period_s=0.05).start()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
     launches = 0
