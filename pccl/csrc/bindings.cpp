@@ -448,11 +448,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     PCCL_CUDA(cudaMemcpy((void*)addr, &v, 4, cudaMemcpyHostToDevice));
     PCCL_CUDA(cudaDeviceSynchronize());
   });
-  m.def("_throw_test", [](int k) {
-    if (k == 0) throw pccl::Error("pccl error");
-    if (k == 1) TORCH_CHECK(false, "torch check");
-    if (k == 2) throw std::runtime_error("runtime error");
-  });
   m.def("num_steps", [](int algo, int P) { return num_steps(algo, P); });
   m.def("ag_step", [](int algo, int P, int r, int t) { return step_tuple(ag_step(algo, P, r, t)); });
   m.def("rs_step", [](int algo, int P, int r, int t) { return step_tuple(rs_step(algo, P, r, t)); });
