@@ -58,6 +58,7 @@ def main():
     ap.add_argument("--fused", action="store_true")
     ap.add_argument("--gather-ctas", type=int, default=16)
     ap.add_argument("--shapes", default=",".join(SHAPES))
+    ap.add_argument("--one-sm", action="store_true", help="use the one-CTA-per-tile form instead of CTA pairs")
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     rank, world, _ = init_distributed()
@@ -82,17 +83,17 @@ def main():
         if not args.fused:
             W = (torch.randn(N, K, device=dev, generator=g) * 0.02).to(torch.bfloat16)
             out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-            ms_ours = timed(lambda: pccl._C.gemm(A, W, None, out))
+            ms_ours = timed(lambda: pccl._C.gemm(A, W, None, out, not args.one_sm))
             ms_ref = timed(lambda: torch.matmul(A, W.t(), out=out))
-            y, err = pccl._C.gemm(A, W, None, None)
+            y, err = pccl._C.gemm(A, W, None, None, not args.one_sm)
             ok = int(err.item()) == 0 and float((y.float() - (A.float() @ W.float().t())).abs().max()) < 0.5
             row = {"shape": name, "M": M, "N": N, "K": K, "tcgen05_ms": ms_ours, "cublas_ms": ms_ref,
                    "tcgen05_tflops": flops / ms_ours / 1e9, "cublas_tflops": flops / ms_ref / 1e9,
-                   "frac_of_measured_peak": flops / ms_ours / 1e9 / peak, "correct": ok}
+                   "frac_of_measured_peak": flops / ms_ours / 1e9 / peak, "cta_pair": not args.one_sm, "correct": ok}
         else:
             if N % (world * 256) != 0:
                 continue
-            lin = AllGatherLinear(comm, None, N, K, gather_ctas=args.gather_ctas)
+            lin = AllGatherLinear(comm, None, N, K, gather_ctas=args.gather_ctas, two_cta=not args.one_sm)
             lin.w_shard.copy_((torch.randn(N // world, K, device=dev, generator=g) * 0.02).to(torch.bfloat16))
             torch.cuda.synchronize()
             dist.barrier()
@@ -114,7 +115,7 @@ def main():
             t_link = remote / 770e9 * 1e3
             row = {"shape": name, "M": M, "N": N, "K": K, "P": world, "fused_ms": ms_ours, "nccl_plus_cublas_ms": ms_ref,
                    "roofline_ms": max(t_math, t_link), "frac_of_roofline": max(t_math, t_link) / ms_ours,
-                   "speedup_vs_baseline": ms_ref / ms_ours, "gather_ctas": args.gather_ctas, "correct": bool(ok)}
+                   "speedup_vs_baseline": ms_ref / ms_ours, "gather_ctas": args.gather_ctas, "cta_pair": not args.one_sm, "correct": bool(ok)}
             del lin
         rows.append(row)
         if rank == 0:

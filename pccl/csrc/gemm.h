@@ -29,6 +29,8 @@ struct GemmArgs {
   void* C;              // [M,N] bf16 row-major, N % 8 == 0
   const void* bias;     // [N] bf16 or nullptr
   int* error;           // device int, set non-zero when a bounded wait ran out
+  int two_cta;          // use the 2-SM MMA form (cta_group::2, one 256x256 tile per CTA pair); fused mode
+                        // then needs an even gather_ctas (gatherers are whole pairs)
   // ---- fused all-gather (gather_ctas == 0: plain GEMM)
   int gather_ctas;      // CTAs that move shards instead of multiplying
   GroupDev g;           // group, epoch, flags (filled by Comm::begin_call)

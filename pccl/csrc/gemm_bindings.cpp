@@ -46,7 +46,7 @@ void fill_common(GemmArgs& a, const at::Tensor& A, const at::Tensor& C, const st
 
 // C = A @ W^T (+ bias).  Returns (C, error flag tensor): error stays 0 unless a bounded wait ran out.
 std::tuple<at::Tensor, at::Tensor> gemm(const at::Tensor& A, const at::Tensor& W, std::optional<at::Tensor> bias,
-                                        std::optional<at::Tensor> out) {
+                                        std::optional<at::Tensor> out, bool two_cta) {
   check_bf16_2d(A, "A");
   check_bf16_2d(W, "W");
   TORCH_CHECK(A.size(1) == W.size(1), "A is [M,K], W is [N,K]: K differs");
@@ -60,6 +60,7 @@ std::tuple<at::Tensor, at::Tensor> gemm(const at::Tensor& A, const at::Tensor& W
   GemmArgs a;
   fill_common(a, A, C, bias, N, K, err);
   a.W = W.data_ptr();
+  a.two_cta = two_cta ? 1 : 0;
   PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), at::cuda::getCurrentCUDAStream().stream()));
   return {C, err};
 }
@@ -68,7 +69,7 @@ std::tuple<at::Tensor, at::Tensor> gemm(const at::Tensor& A, const at::Tensor& W
 // the symmetric heap; w_full: local [N, K] buffer that receives the gathered weight.
 std::tuple<at::Tensor, at::Tensor> ag_gemm(Comm& c, int gid, const at::Tensor& A, const at::Tensor& w_shard,
                                            at::Tensor& w_full, std::optional<at::Tensor> bias,
-                                           std::optional<at::Tensor> out, int gather_ctas) {
+                                           std::optional<at::Tensor> out, int gather_ctas, bool two_cta) {
   check_bf16_2d(A, "A");
   check_bf16_2d(w_shard, "w_shard");
   check_bf16_2d(w_full, "w_full");
@@ -89,7 +90,8 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm(Comm& c, int gid, const at::Tensor& A
   GemmArgs a;
   fill_common(a, A, C, bias, N, K, err);
   a.W = w_full.data_ptr();
-  a.gather_ctas = P > 1 ? std::max(1, gather_ctas) : 0;
+  a.gather_ctas = P > 1 ? std::max(two_cta ? 2 : 1, two_cta ? (gather_ctas + 1) / 2 * 2 : gather_ctas) : 0;
+  a.two_cta = two_cta ? 1 : 0;
   a.shard_off = (uint64_t)off;
   a.panel_flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
@@ -106,7 +108,8 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm(Comm& c, int gid, const at::Tensor& A
 
 // Same kernel with peers that are plain local buffers and no handshake: for tests on one GPU.
 std::tuple<at::Tensor, at::Tensor> ag_gemm_local(const at::Tensor& A, std::vector<at::Tensor> shards, int me,
-                                                 at::Tensor& w_full, std::optional<at::Tensor> bias, int gather_ctas) {
+                                                 at::Tensor& w_full, std::optional<at::Tensor> bias, int gather_ctas,
+                                                 bool two_cta) {
   check_bf16_2d(A, "A");
   check_bf16_2d(w_full, "w_full");
   const int P = (int)shards.size();
@@ -120,7 +123,8 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm_local(const at::Tensor& A, std::vecto
   GemmArgs a;
   fill_common(a, A, C, bias, N, K, err);
   a.W = w_full.data_ptr();
-  a.gather_ctas = std::max(1, gather_ctas);
+  a.gather_ctas = std::max(two_cta ? 2 : 1, two_cta ? (gather_ctas + 1) / 2 * 2 : gather_ctas);
+  a.two_cta = two_cta ? 1 : 0;
   a.shard_off = 0;
   a.panel_flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
   a.g.size = P;
@@ -140,14 +144,15 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm_local(const at::Tensor& A, std::vecto
 
 void bind_gemm(py::module_& m) {
   m.def("gemm", &gemm, py::arg("A"), py::arg("W"), py::arg("bias") = py::none(), py::arg("out") = py::none(),
+        py::arg("two_cta") = true,
         "C = A @ W^T (+bias) on the tcgen05 tensor cores; returns (C, error_flag)");
   m.def("ag_gemm_local", &ag_gemm_local, py::arg("A"), py::arg("shards"), py::arg("me"), py::arg("w_full"),
-        py::arg("bias") = py::none(), py::arg("gather_ctas") = 8);
+        py::arg("bias") = py::none(), py::arg("gather_ctas") = 8, py::arg("two_cta") = true);
   m.def("ag_gemm",
         [](std::shared_ptr<Comm> c, int gid, const at::Tensor& A, const at::Tensor& w_shard, at::Tensor& w_full,
-           std::optional<at::Tensor> bias, std::optional<at::Tensor> out, int gather_ctas) {
-          return ag_gemm(*c, gid, A, w_shard, w_full, bias, out, gather_ctas);
+           std::optional<at::Tensor> bias, std::optional<at::Tensor> out, int gather_ctas, bool two_cta) {
+          return ag_gemm(*c, gid, A, w_shard, w_full, bias, out, gather_ctas, two_cta);
         },
         py::arg("comm"), py::arg("gid"), py::arg("A"), py::arg("w_shard"), py::arg("w_full"), py::arg("bias") = py::none(),
-        py::arg("out") = py::none(), py::arg("gather_ctas") = 16);
+        py::arg("out") = py::none(), py::arg("gather_ctas") = 16, py::arg("two_cta") = true);
 }

@@ -453,6 +453,280 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 }
 
+// ---------------------------------------------------------------- 2-SM variant (cta_group::2)
+// A pair of CTAs on neighbouring SMs works on one 256x256 tile.  Each CTA stages its own
+// 128 rows of A and its own 128 rows of W (32 KiB per stage instead of 48, six stages), the
+// leader CTA issues M=256 MMAs that read both CTAs' shared memory, and each CTA keeps the
+// accumulator rows of its half in its own TMEM.  Per FLOP a third less shared-memory traffic
+// than the single-SM form.  Loads are plain tiled TMA loads (no cluster multicast); both
+// CTAs' loads count on the leader's barrier; commits are sent to each CTA's barrier in turn.
+constexpr int kStages2 = 6;
+constexpr uint32_t kHalfBytes = 128 * BK * 2;              // 16 KiB: 128 rows x 64 bf16
+constexpr uint32_t kStage2Bytes = 2 * kHalfBytes;          // A half + W half
+constexpr uint32_t kBar2Off = kStages2 * kStage2Bytes;     // 196,608
+constexpr uint32_t kIdesc2 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory variable in another CTA of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void mma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc2), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_sm100_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+                           const __grid_constant__ CUtensorMap tmWown, const __grid_constant__ GemmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  if ((int)blockIdx.x < a.gather_ctas) {      // whole pairs: gather_ctas is even
+    gather_role(a, smem, (int)blockIdx.x);
+    return;
+  }
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = ((int)blockIdx.x - a.gather_ctas) >> 1, npairs = ((int)gridDim.x - a.gather_ctas) >> 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kBar2Off);
+  uint64_t* empty = full + kStages2;
+  uint64_t* tmem_full = empty + kStages2;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tmem_full + i, 1);
+      mbar_init(tmem_empty + i, 8);        // four epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                       // both CTAs' barriers exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (a.M + 255) / 256, tiles_n = (a.N + 255) / 256;
+  const int total = tiles_m * tiles_n;
+  const bool fused = a.gather_ctas > 0;
+  const int group_m = fused ? tiles_m : (tiles_m < 8 ? tiles_m : 8);
+  const int nkb = (a.K + BK - 1) / BK;
+  const int P = a.g.size, me = a.g.first_local;
+  const int tpr = fused ? (a.N / P) / BN : 0;            // 256-row panels per rank
+  auto decode = [&](int t, int* m_idx, int* n_idx) {
+    const int band_tiles = group_m * tiles_n;
+    const int band = t / band_tiles;
+    const int first_m = band * group_m;
+    const int rows = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
+    const int in_band = t - band * band_tiles;
+    const int q = in_band / rows;
+    *m_idx = first_m + in_band - q * rows;
+    // fused: own panels first, then the peers' in the order in which they arrive
+    *n_idx = fused ? ((me + q / tpr) % P) * tpr + q % tpr : q;
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = pair; t < total && ok; t += npairs) {
+      int m_idx, n_idx;
+      decode(t, &m_idx, &n_idx);
+      const CUtensorMap* wmap = &tmW;
+      int wy = n_idx * 256 + (int)rank * 128;
+      if (fused) {
+        const int owner = n_idx / tpr;
+        if (owner == me) {
+          wmap = &tmWown;                                   // straight from the shard
+          wy = (n_idx - owner * tpr) * 256 + (int)rank * 128;
+        } else {
+          const uint32_t* flag = a.panel_flags + n_idx;
+          const uint64_t t0 = global_timer_ns();
+          uint32_t spins = 0;
+          for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v >= (uint32_t)a.gather_ctas) break;
+            if ((++spins & 63u) == 0u) {
+              if (*abort_flag != 0 || global_timer_ns() - t0 > kWaitNs) {
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+          }
+          if (!ok) {
+            atomicCAS(a.error, 0, kErrPanel);
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+      }
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const uint32_t s = it % kStages2, ph = (it / kStages2) & 1u;
+        if (!gemm_wait(empty + s, ph ^ 1u, abort_flag)) {
+          ok = false;
+          atomicCAS(a.error, 0, kErrProducer);
+          break;
+        }
+        unsigned char* sa = smem + (size_t)s * kStage2Bytes;
+        if (leader) mbar_expect_tx(full + s, 2 * kStage2Bytes);     // both CTAs' bytes land on this barrier
+        const uint32_t bar = map_to_cta(smem_u32(full + s), 0);      // the leader's barrier, from either CTA
+        tma_load_2d_pair(sa, &tmA, kb * BK, m_idx * 256 + (int)rank * 128, bar);
+        tma_load_2d_pair(sa + kHalfBytes, wmap, kb * BK, wy, bar);
+      }
+    }
+    if (!ok) *abort_flag = 1;
+  } else if (warp == 1 && lane == 0 && leader) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    uint32_t it = 0, tile_count = 0;
+    bool ok = true;
+    for (int t = pair; t < total && ok; t += npairs, ++tile_count) {
+      const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
+      if (!gemm_wait(tmem_empty + acc, acc_ph ^ 1u, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const uint32_t s = it % kStages2, ph = (it / kStages2) & 1u;
+        if (!gemm_wait(full + s, ph, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + (size_t)s * kStage2Bytes);
+        const uint64_t da = smem_desc(sa), db = smem_desc(sa + kHalfBytes);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          mma_bf16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb > 0 || k > 0) ? 1u : 0u);
+        const uint32_t eb = smem_u32(empty + s);
+        mma_commit_pair(map_to_cta(eb, 0));     // free the stage in both CTAs
+        mma_commit_pair(map_to_cta(eb, 1));
+      }
+      if (!ok) break;
+      const uint32_t fb = smem_u32(tmem_full + acc);
+      mma_commit_pair(map_to_cta(fb, 0));       // accumulator complete: wake both epilogues
+      mma_commit_pair(map_to_cta(fb, 1));
+    }
+    if (!ok) {
+      atomicCAS(a.error, 0, kErrMma);
+      *abort_flag = 1;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    uint32_t tile_count = 0;
+    bool ok = true;
+    const int lane_base = (warp & 3) * 32;
+    __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(a.C);
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
+    for (int t = pair; t < total && ok; t += npairs, ++tile_count) {
+      int m_idx, n_idx;
+      decode(t, &m_idx, &n_idx);
+      const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
+      if (!gemm_wait(tmem_full + acc, acc_ph, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = m_idx * 256 + (int)rank * 128 + lane_base + lane;
+      const uint32_t t_base = tmem_base + acc * BN + ((uint32_t)lane_base << 16);
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld32(t_base + cc * 32, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int col0 = n_idx * 256 + cc * 32;
+        if (row < a.M && col0 < a.N) {
+          __nv_bfloat16* out = C + (size_t)row * a.N + col0;
+          if (col0 + 32 <= a.N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
+                if (bias != nullptr) {
+                  x0 += __bfloat162float(bias[col0 + v * 8 + 2 * e]);
+                  x1 += __bfloat162float(bias[col0 + v * 8 + 2 * e + 1]);
+                }
+                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                w[e] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(out + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (col0 + e < a.N) {
+                float x = __uint_as_float(r[e]);
+                if (bias != nullptr) x += __bfloat162float(bias[col0 + e]);
+                out[e] = __float2bfloat16_rn(x);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));   // tell the leader's MMA issuer
+    }
+    if (!ok && lane == 0) {
+      atomicCAS(a.error, 0, kErrEpilogue);
+      *abort_flag = 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                       // the peer may still be reading this CTA's shared memory or signalling it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
 // ---------------------------------------------------------------- host side
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -498,6 +772,26 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a, int sm_count, cudaStream_t stre
     own = a.g.heap[a.g.first_local] + a.shard_off;
     own_rows = (uint64_t)a.N / P;
     if (reinterpret_cast<uintptr_t>(own) & 15u) return cudaErrorInvalidValue;
+  }
+  if (a.two_cta && (a.gather_ctas % 2) == 0) {
+    CUtensorMap mA, mW, mOwn;
+    if (!make_map(&mA, a.A, (uint64_t)a.M, (uint64_t)a.K, 128)) return cudaErrorInvalidValue;
+    if (!make_map(&mW, a.W, (uint64_t)a.N, (uint64_t)a.K, 128)) return cudaErrorInvalidValue;
+    if (!make_map(&mOwn, own, own_rows, (uint64_t)a.K, 128)) return cudaErrorInvalidValue;
+    static thread_local bool configured2[64] = {false};
+    int dev2 = 0;
+    cudaGetDevice(&dev2);
+    if (dev2 < 0 || dev2 >= 64 || !configured2[dev2]) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_sm100_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+      if (e != cudaSuccess) return e;
+      if (dev2 >= 0 && dev2 < 64) configured2[dev2] = true;
+    }
+    const int tiles2 = ((a.M + 255) / 256) * ((a.N + 255) / 256);
+    int pairs = (sm_count - a.gather_ctas) / 2;
+    if (a.gather_ctas == 0 && tiles2 < pairs) pairs = tiles2;
+    if (pairs < 1) return cudaErrorInvalidValue;
+    gemm_sm100_2cta_kernel<<<a.gather_ctas + pairs * 2, kGemmThreads, kGemmSmem, stream>>>(mA, mW, mOwn, a);
+    return cudaGetLastError();
   }
   CUtensorMap tmA, tmW, tmWown;
   if (!make_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM)) return cudaErrorInvalidValue;

@@ -28,7 +28,7 @@ def _C():
 
 class AllGatherLinear:
     def __init__(self, comm: Communicator, group: Optional[Group], out_features: int, in_features: int,
-                 gather_ctas: int = 16, device=None):
+                 gather_ctas: int = 16, device=None, two_cta: bool = True):
         self.comm = comm
         self.group = group or comm.world_group
         P = self.group.size
@@ -38,6 +38,7 @@ class AllGatherLinear:
             raise ValueError("in_features must be a multiple of 8")
         self.N, self.K, self.P = out_features, in_features, P
         self.gather_ctas = gather_ctas
+        self.two_cta = two_cta       # multiply with CTA pairs (cta_group::2, 256x256 tiles)
         self.w_shard = comm.empty((out_features // P, in_features), torch.bfloat16)
         dev = device or self.w_shard.device
         self.w_full = torch.empty((out_features, in_features), dtype=torch.bfloat16, device=dev)
@@ -46,7 +47,7 @@ class AllGatherLinear:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.K)
         y, err = _C().ag_gemm(self.comm.native, self.group.gid, x2, self.w_shard, self.w_full, bias, None,
-                              self.gather_ctas)
+                              self.gather_ctas, self.two_cta)
         if check:
             code = int(err.item())
             self.comm.check(sync=False)

@@ -20,19 +20,20 @@ def check_close(y, ref, K):
     assert float(rel) < 5e-3, f"relative error {float(rel):.3e}"
 
 
+@pytest.mark.parametrize("two_cta", [False, True], ids=["one_sm", "cta_pair"])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 128), (384, 768, 2048), (1000, 520, 328), (8192, 6144, 2048)])
-def test_gemm_matches_fp32_reference(shape):
+def test_gemm_matches_fp32_reference(shape, two_cta):
     import pccl
 
     M, N, K = shape
     A, W = rnd((M, K), 1), rnd((N, K), 2, 0.05)
     bias = rnd((N,), 3)
-    y, err = pccl._C.gemm(A, W, bias, None)
+    y, err = pccl._C.gemm(A, W, bias, None, two_cta)
     torch.cuda.synchronize()
     assert int(err.item()) == 0
     ref = A.float() @ W.float().t() + bias.float()
     check_close(y, ref, K)
-    y2, err2 = pccl._C.gemm(A, W, None, None)
+    y2, err2 = pccl._C.gemm(A, W, None, None, two_cta)
     torch.cuda.synchronize()
     assert int(err2.item()) == 0
     check_close(y2, A.float() @ W.float().t(), K)
@@ -53,8 +54,9 @@ def test_linear_wrapper_and_identity():
         linear(rnd((4, 12), 1), rnd((8, 12), 2))   # K not a multiple of 8
 
 
+@pytest.mark.parametrize("two_cta", [False, True], ids=["one_sm", "cta_pair"])
 @pytest.mark.parametrize("P,me", [(2, 0), (4, 3), (8, 5)])
-def test_fused_gather_gemm_with_local_peers(P, me):
+def test_fused_gather_gemm_with_local_peers(P, me, two_cta):
     """The fused kernel with peers that are local buffers: gatherer CTAs pull every shard
     into the local weight buffer while the GEMM CTAs multiply panel by panel."""
     import pccl
@@ -65,7 +67,7 @@ def test_fused_gather_gemm_with_local_peers(P, me):
     shards = [rnd((N // P, K), 20 + p, 0.05) for p in range(P)]
     bias = rnd((N,), 40)
     w_full = torch.zeros((N, K), device=DEV, dtype=torch.bfloat16)
-    y, err = pccl._C.ag_gemm_local(A, shards, me, w_full, bias, 4)
+    y, err = pccl._C.ag_gemm_local(A, shards, me, w_full, bias, 4, two_cta)
     torch.cuda.synchronize()
     assert int(err.item()) == 0
     W = torch.cat(shards)
