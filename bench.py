@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--nvls", type=int, default=int(os.environ.get("PCCL_ENABLE_NVLS", "0")))
     ap.add_argument("--fused-ag-gemm", type=int, default=int(os.environ.get("PCCL_FUSED_AG_GEMM", "0")))
     ap.add_argument("--gather-ctas", type=int, default=16)
+    ap.add_argument("--fused-gelu-gemm", type=int, default=int(os.environ.get("PCCL_FUSED_GELU_GEMM", "0")),
+                    help="FC1 on the library's tcgen05 GEMM with bias+GELU in the epilogue")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 
@@ -104,7 +106,8 @@ def main() -> None:
         patch_deepspeed(world, algorithm=args.algorithm, lanes=args.lanes)
     backend = TorchBackend()
     engine = Zero3Engine(cfg, backend, OptimConfig(), device=dev, comm=comm, micro_batch=mb,
-                         fused_ag_gemm=(args.impl == "pccl" and bool(args.fused_ag_gemm)), gather_ctas=args.gather_ctas)
+                         fused_ag_gemm=(args.impl == "pccl" and bool(args.fused_ag_gemm)), gather_ctas=args.gather_ctas,
+                         fused_gelu_gemm=bool(args.fused_gelu_gemm))
 
     total_steps = warmup + args.steps
     gen = torch.Generator(device="cpu").manual_seed(4321 + rank)
@@ -141,8 +144,7 @@ def main() -> None:
     ms = max_over_ranks(t_start.elapsed_time(t_end) / args.steps)
     tokens_per_step = world * mb * S
     value = tokens_per_step / (ms / 1e3)
-    if comm is not None:
-        comm.check()
+    engine.check_errors()                               # raises if any kernel gave up in a bounded wait
 
     e2e = None
     if not args.no_e2e:
@@ -189,7 +191,7 @@ def main() -> None:
                 "global_batch": world * mb, "micro_batch_per_gpu": mb, "seq_len": S,
                 "parallelism": f"zero3-dp{world}", "optimizer": "AdamW fp32 master+moments, grad-norm clip 1.0",
                 "algorithm": args.algorithm, "lanes": args.lanes, "nvls": bool(args.nvls),
-                "fused_ag_gemm": bool(engine.fused_ag_gemm),
+                "fused_ag_gemm": bool(engine.fused_ag_gemm), "fused_gelu_gemm": bool(engine.fused_gelu_gemm),
                 "l2": "working set per step (tens of GB) exceeds the 126 MB L2; no explicit flush",
                 "transport": comm.transport_name if comm is not None else "nccl",
             },

@@ -28,6 +28,7 @@ struct GemmArgs {
   const void* W;        // [N,K] bf16 row-major (plain mode: the weight; fused mode: the local gather buffer)
   void* C;              // [M,N] bf16 row-major, N % 8 == 0
   const void* bias;     // [N] bf16 or nullptr
+  void* act_out;        // [M,N] bf16 or nullptr: second output, gelu(C) in the tanh form (C keeps the pre-activation)
   int* error;           // device int, set non-zero when a bounded wait ran out
   int two_cta;          // use the 2-SM MMA form (cta_group::2, one 256x256 tile per CTA pair); fused mode
                         // then needs an even gather_ctas (gatherers are whole pairs)

@@ -65,6 +65,28 @@ std::tuple<at::Tensor, at::Tensor> gemm(const at::Tensor& A, const at::Tensor& W
   return {C, err};
 }
 
+// U = A @ W^T + bias and G = gelu(U) from one kernel: the first linear layer of a transformer MLP
+// with its activation in the epilogue.  Returns (U, G, error flag); the backward pass needs both.
+std::tuple<at::Tensor, at::Tensor, at::Tensor> gemm_gelu(const at::Tensor& A, const at::Tensor& W,
+                                                         std::optional<at::Tensor> bias, bool two_cta) {
+  check_bf16_2d(A, "A");
+  check_bf16_2d(W, "W");
+  TORCH_CHECK(A.size(1) == W.size(1), "A is [M,K], W is [N,K]: K differs");
+  const int N = (int)W.size(0), K = (int)W.size(1);
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0, "K and N must be multiples of 8");
+  c10::cuda::CUDAGuard guard(A.device());
+  at::Tensor U = at::empty({A.size(0), N}, A.options());
+  at::Tensor G = at::empty({A.size(0), N}, A.options());
+  at::Tensor err = at::zeros({1}, A.options().dtype(at::kInt));
+  GemmArgs a;
+  fill_common(a, A, U, bias, N, K, err);
+  a.W = W.data_ptr();
+  a.act_out = G.data_ptr();
+  a.two_cta = two_cta ? 1 : 0;
+  PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), at::cuda::getCurrentCUDAStream().stream()));
+  return {U, G, err};
+}
+
 // Fused all-gather + GEMM on a communicator group.  w_shard: this rank's [N/P, K] rows, in
 // the symmetric heap; w_full: local [N, K] buffer that receives the gathered weight.
 std::tuple<at::Tensor, at::Tensor> ag_gemm(Comm& c, int gid, const at::Tensor& A, const at::Tensor& w_shard,
@@ -146,6 +168,8 @@ void bind_gemm(py::module_& m) {
   m.def("gemm", &gemm, py::arg("A"), py::arg("W"), py::arg("bias") = py::none(), py::arg("out") = py::none(),
         py::arg("two_cta") = true,
         "C = A @ W^T (+bias) on the tcgen05 tensor cores; returns (C, error_flag)");
+  m.def("gemm_gelu", &gemm_gelu, py::arg("A"), py::arg("W"), py::arg("bias") = py::none(), py::arg("two_cta") = true,
+        "(U, gelu(U), error_flag) with U = A @ W^T (+bias): activation fused into the GEMM epilogue");
   m.def("ag_gemm_local", &ag_gemm_local, py::arg("A"), py::arg("shards"), py::arg("me"), py::arg("w_full"),
         py::arg("bias") = py::none(), py::arg("gather_ctas") = 8, py::arg("two_cta") = true);
   m.def("ag_gemm",

@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 
 #include "bulk.cuh"
+#include "act.cuh"
 #include "gemm.h"
 #include "primitives.cuh"
 
@@ -245,6 +246,55 @@ __device__ void gather_role(const GemmArgs& a, unsigned char* smem, int gi) {
   }
 }
 
+// Epilogue of one accumulator row segment: 32 fp32 values of row `row`, columns col0..col0+31.
+// Adds the bias, rounds to bf16 and stores; with act_out it also stores gelu() of the rounded
+// value (what a separate activation kernel would read) to the second output.
+__device__ __forceinline__ void epilogue_store32(const GemmArgs& a, const uint32_t (&r)[32], int row, int col0) {
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.C) + (size_t)row * a.N + col0;
+  __nv_bfloat16* act = a.act_out != nullptr ? reinterpret_cast<__nv_bfloat16*>(a.act_out) + (size_t)row * a.N + col0 : nullptr;
+  const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
+  if (col0 + 32 <= a.N) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (bias != nullptr) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(bias + col0 + v * 8));     // N % 8 == 0: 16-byte aligned
+        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          b[2 * e] = __uint_as_float(qw[e] << 16);
+          b[2 * e + 1] = __uint_as_float(qw[e] & 0xffff0000u);
+        }
+      }
+      uint32_t w[4], g[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x0 = __uint_as_float(r[v * 8 + 2 * e]) + b[2 * e], x1 = __uint_as_float(r[v * 8 + 2 * e + 1]) + b[2 * e + 1];
+        __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+        w[e] = *reinterpret_cast<uint32_t*>(&h);
+        if (act != nullptr) {
+          __nv_bfloat162 hg = __floats2bfloat162_rn(gelu_tanh(__low2float(h)), gelu_tanh(__high2float(h)));
+          g[e] = *reinterpret_cast<uint32_t*>(&hg);
+        }
+      }
+      *reinterpret_cast<uint4*>(out + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (act != nullptr) *reinterpret_cast<uint4*>(act + v * 8) = make_uint4(g[0], g[1], g[2], g[3]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      if (col0 + e < a.N) {
+        float x = __uint_as_float(r[e]);
+        if (bias != nullptr) x += __bfloat162float(bias[col0 + e]);
+        const __nv_bfloat16 h = __float2bfloat16_rn(x);
+        out[e] = h;
+        if (act != nullptr) act[e] = __float2bfloat16_rn(gelu_tanh(__bfloat162float(h)));
+      }
+    }
+  }
+}
+
+
 // ---------------------------------------------------------------- the kernel
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
@@ -387,8 +437,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint32_t tile_count = 0;
     bool ok = true;
     const int lane_base = (warp & 3) * 32;
-    __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(a.C);
-    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
     for (int t = cta; t < sch.total && ok; t += ncta, ++tile_count) {
       int m_idx, n_idx;
       sch.decode(t, &m_idx, &n_idx);
@@ -406,35 +454,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         tmem_ld32(t_base + cc * 32, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int col0 = n_idx * BN + cc * 32;
-        if (row < a.M && col0 < a.N) {
-          __nv_bfloat16* out = C + (size_t)row * a.N + col0;
-          if (col0 + 32 <= a.N) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
-                if (bias != nullptr) {
-                  x0 += __bfloat162float(bias[col0 + v * 8 + 2 * e]);
-                  x1 += __bfloat162float(bias[col0 + v * 8 + 2 * e + 1]);
-                }
-                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                w[e] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(out + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              if (col0 + e < a.N) {
-                float x = __uint_as_float(r[e]);
-                if (bias != nullptr) x += __bfloat162float(bias[col0 + e]);
-                out[e] = __float2bfloat16_rn(x);
-              }
-            }
-          }
-        }
+        if (row < a.M && col0 < a.N) epilogue_store32(a, r, row, col0);
       }
       tc_fence_before();
       __syncwarp();
@@ -455,15 +475,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
 // ---------------------------------------------------------------- 2-SM variant (cta_group::2)
 // A pair of CTAs on neighbouring SMs works on one 256x256 tile.  Each CTA stages its own
-// 128 rows of A and its own 128 rows of W (32 KiB per stage instead of 48, six stages), the
+// 128 rows of A and its own 128 rows of W (32 KiB per stage instead of 48, seven stages), the
 // leader CTA issues M=256 MMAs that read both CTAs' shared memory, and each CTA keeps the
 // accumulator rows of its half in its own TMEM.  Per FLOP a third less shared-memory traffic
 // than the single-SM form.  Loads are plain tiled TMA loads (no cluster multicast); both
 // CTAs' loads count on the leader's barrier; commits are sent to each CTA's barrier in turn.
-constexpr int kStages2 = 6;
+constexpr int kStages2 = 7;
 constexpr uint32_t kHalfBytes = 128 * BK * 2;              // 16 KiB: 128 rows x 64 bf16
 constexpr uint32_t kStage2Bytes = 2 * kHalfBytes;          // A half + W half
-constexpr uint32_t kBar2Off = kStages2 * kStage2Bytes;     // 196,608
+constexpr uint32_t kBar2Off = kStages2 * kStage2Bytes;     // 229,376
+constexpr uint32_t kGemm2Smem = kBar2Off + 256 + 1024;     // 230,656 of the 232,448 a CTA may have
+static_assert(kBulkSmemBytes <= kBar2Off + 256, "the gatherer's copy ring must fit");
 constexpr uint32_t kIdesc2 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -660,8 +682,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     uint32_t tile_count = 0;
     bool ok = true;
     const int lane_base = (warp & 3) * 32;
-    __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(a.C);
-    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
     for (int t = pair; t < total && ok; t += npairs, ++tile_count) {
       int m_idx, n_idx;
       decode(t, &m_idx, &n_idx);
@@ -679,35 +699,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         tmem_ld32(t_base + cc * 32, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int col0 = n_idx * 256 + cc * 32;
-        if (row < a.M && col0 < a.N) {
-          __nv_bfloat16* out = C + (size_t)row * a.N + col0;
-          if (col0 + 32 <= a.N) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
-                if (bias != nullptr) {
-                  x0 += __bfloat162float(bias[col0 + v * 8 + 2 * e]);
-                  x1 += __bfloat162float(bias[col0 + v * 8 + 2 * e + 1]);
-                }
-                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                w[e] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(out + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              if (col0 + e < a.N) {
-                float x = __uint_as_float(r[e]);
-                if (bias != nullptr) x += __bfloat162float(bias[col0 + e]);
-                out[e] = __float2bfloat16_rn(x);
-              }
-            }
-          }
-        }
+        if (row < a.M && col0 < a.N) epilogue_store32(a, r, row, col0);
       }
       tc_fence_before();
       __syncwarp();
@@ -782,7 +774,7 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a, int sm_count, cudaStream_t stre
     int dev2 = 0;
     cudaGetDevice(&dev2);
     if (dev2 < 0 || dev2 >= 64 || !configured2[dev2]) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_sm100_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+      cudaError_t e = cudaFuncSetAttribute(gemm_sm100_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemm2Smem);
       if (e != cudaSuccess) return e;
       if (dev2 >= 0 && dev2 < 64) configured2[dev2] = true;
     }
@@ -790,7 +782,7 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a, int sm_count, cudaStream_t stre
     int pairs = (sm_count - a.gather_ctas) / 2;
     if (a.gather_ctas == 0 && tiles2 < pairs) pairs = tiles2;
     if (pairs < 1) return cudaErrorInvalidValue;
-    gemm_sm100_2cta_kernel<<<a.gather_ctas + pairs * 2, kGemmThreads, kGemmSmem, stream>>>(mA, mW, mOwn, a);
+    gemm_sm100_2cta_kernel<<<a.gather_ctas + pairs * 2, kGemmThreads, kGemm2Smem, stream>>>(mA, mW, mOwn, a);
     return cudaGetLastError();
   }
   CUtensorMap tmA, tmW, tmWown;

@@ -28,10 +28,24 @@ int col_sum_row_splits(int64_t T, int N);
 cudaError_t launch_col_sum(const void* X, int64_t T, int N, void* out, float* partial, int* counters, int R,
                            cudaStream_t s);
 
-// Layer-norm backward for bf16 activations with d in {1024, 2048, 4096}: writes dx, dgamma, dbeta.
-// pgamma / pbeta: 2 * ln_bwd_blocks() * d floats of scratch each.
+// du = dg * gelu'(u) (tanh form, bf16, [T, N]) and out[c] = sum over rows of du, in one pass.
+// Scratch as for launch_col_sum.
+cudaError_t launch_gelu_bwd_col_sum(const void* dg, const void* u, void* du, int64_t T, int N, void* out, float* partial,
+                                    int* counters, int R, cudaStream_t s);
+
+// out = gelu(in), tanh form, bf16, n % 8 == 0, both 16-byte aligned.
+cudaError_t launch_gelu_fwd(const void* in, void* out, int64_t n, cudaStream_t s);
+
+// Layer norm over rows of d in {1024, 2048, 4096} bf16 elements.  branch != nullptr: the row is
+// x + branch, written back over branch.  mean / rstd: T floats each.
+cudaError_t launch_ln_fwd(const void* x, void* branch, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                          int64_t T, int d, float eps, cudaStream_t s);
+
+// Layer-norm backward for bf16 activations with d in {1024, 2048, 4096}: writes dx (+ resid when
+// given), dgamma, dbeta.  pgamma / pbeta: ln_bwd_blocks() * d floats of scratch each.
 int ln_bwd_blocks();
 cudaError_t launch_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma, void* dx,
-                          void* dgamma, void* dbeta, float* pgamma, float* pbeta, int64_t T, int d, cudaStream_t s);
+                          const void* resid, void* dgamma, void* dbeta, float* pgamma, float* pbeta, int64_t T, int d,
+                          cudaStream_t s);
 
 }  // namespace pccl

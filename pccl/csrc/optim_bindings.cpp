@@ -3,6 +3,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <optional>
+#include <tuple>
+
 #include "comm.h"
 #include "optim.h"
 
@@ -100,6 +103,7 @@ void col_sum(const at::Tensor& x, at::Tensor& out) {
   c10::cuda::CUDAGuard guard(x.device());
   const int dev = x.get_device();
   const int R = col_sum_row_splits(T, N);
+  TORCH_CHECK((int64_t)R * N <= (int64_t)64 * 8192, "too many columns for the column-sum scratch");
   at::Tensor& part = scratch(dev, (int64_t)R * N);
   at::Tensor& cnt = counters(dev, (N + 63) / 64);
   PCCL_CUDA(launch_col_sum(x.data_ptr(), T, N, out.data_ptr(), part.data_ptr<float>(), cnt.data_ptr<int>(), R,
@@ -108,8 +112,66 @@ void col_sum(const at::Tensor& x, at::Tensor& out) {
 
 bool ln_bwd_supported(int64_t d) { return d == 1024 || d == 2048 || d == 4096; }
 
+// du = dg * gelu'(u), and bias_grad[c] = sum_r du[r, c], in one pass.
+at::Tensor gelu_bwd_col_sum(const at::Tensor& dg, const at::Tensor& u, at::Tensor& bias_grad) {
+  TORCH_CHECK(dg.is_cuda() && dg.dim() == 2 && dg.scalar_type() == at::kBFloat16 && dg.is_contiguous(),
+              "dg must be a contiguous 2-D bfloat16 CUDA tensor");
+  TORCH_CHECK(u.sizes() == dg.sizes() && u.scalar_type() == at::kBFloat16 && u.is_contiguous() && u.device() == dg.device(),
+              "u must match dg");
+  check_flat(bias_grad, "bias_grad", at::kBFloat16);
+  const int64_t T = dg.size(0);
+  const int N = (int)dg.size(1);
+  TORCH_CHECK(bias_grad.numel() == N && N % 8 == 0 && ((uintptr_t)dg.data_ptr()) % 16 == 0 && ((uintptr_t)u.data_ptr()) % 16 == 0,
+              "bias_grad must hold N elements, N % 8 == 0, 16-byte aligned inputs");
+  c10::cuda::CUDAGuard guard(dg.device());
+  const int dev = dg.get_device();
+  at::Tensor du = at::empty_like(dg);
+  const int R = col_sum_row_splits(T, N);
+  TORCH_CHECK((int64_t)R * N <= (int64_t)64 * 8192, "too many columns for the column-sum scratch");
+  at::Tensor& part = scratch(dev, (int64_t)R * N);
+  at::Tensor& cnt = counters(dev, (N + 63) / 64);
+  PCCL_CUDA(launch_gelu_bwd_col_sum(dg.data_ptr(), u.data_ptr(), du.data_ptr(), T, N, bias_grad.data_ptr(),
+                                    part.data_ptr<float>(), cnt.data_ptr<int>(), R, at::cuda::getCurrentCUDAStream().stream()));
+  return du;
+}
+
+at::Tensor gelu(const at::Tensor& u) {
+  TORCH_CHECK(u.is_cuda() && u.scalar_type() == at::kBFloat16 && u.is_contiguous(), "u must be a contiguous bfloat16 CUDA tensor");
+  TORCH_CHECK(u.numel() % 8 == 0 && ((uintptr_t)u.data_ptr()) % 16 == 0, "numel % 8 == 0 and 16-byte alignment required");
+  c10::cuda::CUDAGuard guard(u.device());
+  at::Tensor g = at::empty_like(u);
+  PCCL_CUDA(launch_gelu_fwd(u.data_ptr(), g.data_ptr(), u.numel(), at::cuda::getCurrentCUDAStream().stream()));
+  return g;
+}
+
+// y = layer_norm(x + branch) with the sum written back over branch; branch may be None.
+std::tuple<at::Tensor, at::Tensor, at::Tensor> ln_fwd(const at::Tensor& x, std::optional<at::Tensor> branch,
+                                                      const at::Tensor& gamma, const at::Tensor& beta, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "x: contiguous 2-D bf16");
+  const int64_t T = x.size(0), d = x.size(1);
+  TORCH_CHECK(d == 1024 || d == 2048 || d == 4096, "layer-norm kernel takes d in {1024, 2048, 4096}");
+  check_flat(gamma, "gamma", at::kBFloat16);
+  check_flat(beta, "beta", at::kBFloat16);
+  TORCH_CHECK(gamma.numel() == d && beta.numel() == d, "gamma and beta must hold d elements");
+  TORCH_CHECK(((uintptr_t)x.data_ptr() | (uintptr_t)gamma.data_ptr() | (uintptr_t)beta.data_ptr()) % 16 == 0, "16-byte alignment");
+  void* bptr = nullptr;
+  if (branch.has_value()) {
+    TORCH_CHECK(branch->sizes() == x.sizes() && branch->scalar_type() == at::kBFloat16 && branch->is_contiguous() &&
+                    branch->device() == x.device() && ((uintptr_t)branch->data_ptr()) % 16 == 0,
+                "branch must match x");
+    bptr = branch->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty_like(x);
+  at::Tensor mean = at::empty({T}, x.options().dtype(at::kFloat));
+  at::Tensor rstd = at::empty({T}, x.options().dtype(at::kFloat));
+  PCCL_CUDA(launch_ln_fwd(x.data_ptr(), bptr, gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
+                          rstd.data_ptr<float>(), T, (int)d, (float)eps, at::cuda::getCurrentCUDAStream().stream()));
+  return {y, mean, rstd};
+}
+
 at::Tensor ln_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& mean, const at::Tensor& rstd,
-                  const at::Tensor& gamma, at::Tensor& dgamma, at::Tensor& dbeta) {
+                  const at::Tensor& gamma, at::Tensor& dgamma, at::Tensor& dbeta, std::optional<at::Tensor> resid) {
   TORCH_CHECK(dy.is_cuda() && dy.dim() == 2 && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous(), "dy: 2-D bf16");
   TORCH_CHECK(x.sizes() == dy.sizes() && x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "x must match dy");
   const int64_t T = dy.size(0), d = dy.size(1);
@@ -121,14 +183,21 @@ at::Tensor ln_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& m
   check_flat(dbeta, "dbeta", at::kBFloat16);
   TORCH_CHECK(mean.numel() == T && rstd.numel() == T && gamma.numel() == d && dgamma.numel() == d && dbeta.numel() == d,
               "size mismatch");
+  const void* rptr = nullptr;
+  if (resid.has_value()) {
+    TORCH_CHECK(resid->sizes() == dy.sizes() && resid->scalar_type() == at::kBFloat16 && resid->is_contiguous() &&
+                    resid->device() == dy.device() && ((uintptr_t)resid->data_ptr()) % 16 == 0,
+                "resid must match dy");
+    rptr = resid->data_ptr();
+  }
   c10::cuda::CUDAGuard guard(dy.device());
   const int dev = dy.get_device();
   at::Tensor dx = at::empty_like(dy);
-  const int64_t part = (int64_t)2 * ln_bwd_blocks() * d;
+  const int64_t part = (int64_t)ln_bwd_blocks() * d;
   at::Tensor& sc = scratch(dev, 2 * part + (int64_t)64 * 8192);
   float* pg = sc.data_ptr<float>() + (int64_t)64 * 8192;     // the front of the buffer belongs to col_sum
   PCCL_CUDA(launch_ln_bwd(dy.data_ptr(), x.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr(),
-                          dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), pg, pg + part, T, (int)d,
+                          dx.data_ptr(), rptr, dgamma.data_ptr(), dbeta.data_ptr(), pg, pg + part, T, (int)d,
                           at::cuda::getCurrentCUDAStream().stream()));
   return dx;
 }
@@ -137,7 +206,13 @@ at::Tensor ln_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& m
 
 void bind_optim(py::module_& m) {
   m.def("col_sum", &col_sum, "out[c] = sum_r x[r, c] (bf16 in/out, fp32 accumulation)");
-  m.def("ln_bwd", &ln_bwd, "layer-norm backward: returns dx, writes dgamma and dbeta");
+  m.def("ln_bwd", &ln_bwd, py::arg("dy"), py::arg("x"), py::arg("mean"), py::arg("rstd"), py::arg("gamma"), py::arg("dgamma"),
+        py::arg("dbeta"), py::arg("resid") = py::none(),
+        "layer-norm backward: returns dx (+ resid), writes dgamma and dbeta");
+  m.def("ln_fwd", &ln_fwd, py::arg("x"), py::arg("branch"), py::arg("gamma"), py::arg("beta"), py::arg("eps"),
+        "layer norm of x (+ branch, summed in place into branch): returns (y, mean, rstd)");
+  m.def("gelu", &gelu, "tanh-form GELU, bf16");
+  m.def("gelu_bwd_col_sum", &gelu_bwd_col_sum, "du = dg * gelu'(u); bias_grad = column sums of du");
   m.def("ln_bwd_supported", &ln_bwd_supported);
   m.def("sq_norm", &sq_norm, "out += sum(x*x)");
   m.def("adamw", &adamw, py::arg("master"), py::arg("exp_avg"), py::arg("exp_avg_sq"), py::arg("grad"), py::arg("param"),

@@ -145,12 +145,25 @@ def _default_linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor],
     return F.linear(x, w, b)
 
 
-def _ln_fwd(x, w, b, eps):
-    return torch.ops.aten.native_layer_norm(x, [x.shape[-1]], w, b, eps)
+def _ln_fwd(x, w, b, eps, branch=None):
+    """Layer norm of ``x`` (+ ``branch``).  With ``branch`` the sum is formed in the same pass,
+    written over ``branch`` and returned as the new residual stream: (y, mean, rstd, x_sum)."""
+    if _fast(x) and x.shape[-1] in (1024, 2048, 4096) and w.is_contiguous() and b.is_contiguous() \
+            and (branch is None or _fast(branch)):
+        global native_launches
+        native_launches += 1
+        y, mean, rstd = _kernels().ln_fwd(x, branch, w, b, eps)
+        return y, mean, rstd, (x if branch is None else branch)
+    if branch is not None:
+        x = branch.add_(x)
+    y, mean, rstd = torch.ops.aten.native_layer_norm(x, [x.shape[-1]], w, b, eps)
+    return y, mean, rstd, x
 
 
 _native = None
-native_launches = 0     # kernels of this library launched by the functions below (col_sum, ln_bwd + finalize)
+native_launches = 0     # kernels of this library launched by the functions below
+fused_gelu_gemm = False  # FC1 on the tcgen05 GEMM with the GELU in its epilogue (set by the engine)
+gemm_errors: List[torch.Tensor] = []   # error flags of the GEMM launches above, read by the engine's check
 
 
 def _kernels():
@@ -170,16 +183,19 @@ def _fast(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.is_contiguous() and bool(_kernels())
 
 
-def _ln_bwd(dy, x, mean, rstd, w, b, gw, gb):
-    if _fast(dy) and _fast(x) and x.shape[-1] in (1024, 2048, 4096) and gw.is_contiguous() and gb.is_contiguous():
+def _ln_bwd(dy, x, mean, rstd, w, b, gw, gb, resid=None):
+    """dx of a layer norm (+ ``resid``, the gradient flowing around it); writes gw, gb."""
+    if _fast(dy) and _fast(x) and x.shape[-1] in (1024, 2048, 4096) and gw.is_contiguous() and gb.is_contiguous() \
+            and (resid is None or _fast(resid)):
         # one pass over dy and x: dx plus the weight/bias gradients, written in place
         global native_launches
         native_launches += 2
-        return _kernels().ln_bwd(dy, x, mean.view(-1), rstd.view(-1), w, gw, gb)
-    dx, dw, db = torch.ops.aten.native_layer_norm_backward(dy, x, [x.shape[-1]], mean, rstd, w, b, [True, True, True])
+        return _kernels().ln_bwd(dy, x, mean.view(-1), rstd.view(-1), w, gw, gb, resid)
+    dx, dw, db = torch.ops.aten.native_layer_norm_backward(dy, x, [x.shape[-1]], mean.view(-1, 1), rstd.view(-1, 1), w, b,
+                                                           [True, True, True])
     gw.copy_(dw)
     gb.copy_(db)
-    return dx
+    return dx if resid is None else dx.add_(resid)
 
 
 def _wgrad(dy: torch.Tensor, x: torch.Tensor, gw: torch.Tensor, gb: Optional[torch.Tensor]) -> None:
@@ -193,25 +209,63 @@ def _wgrad(dy: torch.Tensor, x: torch.Tensor, gw: torch.Tensor, gb: Optional[tor
             torch.sum(dy, dim=0, out=gb)
 
 
-def layer_forward(x: torch.Tensor, p: Dict[str, torch.Tensor], cfg: GPTConfig, batch: int,
-                  linear_fwd: LinearFwd = _default_linear):
-    """x: [T, d] with T = batch * seq.  Returns (y, ctx)."""
+def _fc1_gelu(h: torch.Tensor, p: Dict[str, torch.Tensor], linear_fwd: LinearFwd):
+    """u = h @ fc1_w^T + fc1_b and g = gelu(u)."""
+    global native_launches
+    w, b = p["fc1_w"], p["fc1_b"]
+    if fused_gelu_gemm and linear_fwd is _default_linear and _fast(h) and _fast(w) and b.is_contiguous() \
+            and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
+        native_launches += 1
+        u, g, err = _kernels().gemm_gelu(h, w, b)
+        gemm_errors.append(err)
+        return u, g
+    u = linear_fwd(h, w, b, "fc1")
+    if _fast(u) and u.numel() % 8 == 0:
+        native_launches += 1
+        return u, _kernels().gelu(u)
+    return u, F.gelu(u, approximate="tanh")
+
+
+def _gelu_bwd(dg: torch.Tensor, u: torch.Tensor, gb: torch.Tensor) -> torch.Tensor:
+    """du = dg * gelu'(u); the bias gradient of the layer in front (column sums of du) goes to gb."""
+    if _fast(dg) and _fast(u) and u.shape[1] % 8 == 0 and gb.is_contiguous():
+        global native_launches
+        native_launches += 1
+        return _kernels().gelu_bwd_col_sum(dg, u, gb)
+    du = torch.ops.aten.gelu_backward(dg, u, approximate="tanh")
+    torch.sum(du, dim=0, out=gb)
+    return du
+
+
+def layer_forward_deferred(x: torch.Tensor, branch: Optional[torch.Tensor], p: Dict[str, torch.Tensor], cfg: GPTConfig,
+                           batch: int, linear_fwd: LinearFwd = _default_linear):
+    """One transformer block whose residual adds ride on the layer norms.
+
+    The block's input is ``x + branch`` (``branch``: the previous block's MLP output, not yet
+    added; None for the first block).  Returns ``(x2, mlp_out, ctx)``: the block's output is
+    ``x2 + mlp_out``, left unsummed so the next layer norm adds it in its own pass."""
     T, d = x.shape
     S, H, dh = T // batch, cfg.n_head, cfg.head_dim
-    h1, mean1, rstd1 = _ln_fwd(x, p["ln1_w"], p["ln1_b"], cfg.ln_eps)
+    h1, mean1, rstd1, x = _ln_fwd(x, p["ln1_w"], p["ln1_b"], cfg.ln_eps, branch)
     qkv = linear_fwd(h1, p["qkv_w"], p["qkv_b"], "qkv")                  # [T, 3d]
     q, k, v = (t.transpose(1, 2) for t in qkv.view(batch, S, 3, H, dh).unbind(2))   # [B, H, S, dh] views
     qd, kd, vd = (t.detach().requires_grad_() for t in (q, k, v))
     with torch.enable_grad():
         att = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True)            # [B, H, S, dh]
     a = att.detach().transpose(1, 2).reshape(T, d)
-    x2 = torch.addmm(p["proj_b"], a, p["proj_w"].t()).add_(x)
-    h2, mean2, rstd2 = _ln_fwd(x2, p["ln2_w"], p["ln2_b"], cfg.ln_eps)
-    u = linear_fwd(h2, p["fc1_w"], p["fc1_b"], "fc1")                    # [T, f]
-    g = F.gelu(u, approximate="tanh")
-    y = torch.addmm(p["fc2_b"], g, p["fc2_w"].t()).add_(x2)
+    o = torch.addmm(p["proj_b"], a, p["proj_w"].t())
+    h2, mean2, rstd2, x2 = _ln_fwd(x, p["ln2_w"], p["ln2_b"], cfg.ln_eps, o)       # x2 = x + o, in o's memory
+    u, g = _fc1_gelu(h2, p, linear_fwd)                                  # [T, f]
+    m = torch.addmm(p["fc2_b"], g, p["fc2_w"].t())
     ctx = (x, mean1, rstd1, h1, qd, kd, vd, att, a, x2, mean2, rstd2, h2, u, g)
-    return y, ctx
+    return x2, m, ctx
+
+
+def layer_forward(x: torch.Tensor, p: Dict[str, torch.Tensor], cfg: GPTConfig, batch: int,
+                  linear_fwd: LinearFwd = _default_linear):
+    """x: [T, d] with T = batch * seq.  Returns (y, ctx)."""
+    x2, m, ctx = layer_forward_deferred(x, None, p, cfg, batch, linear_fwd)
+    return m.add_(x2), ctx
 
 
 def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[str, torch.Tensor], cfg: GPTConfig,
@@ -222,12 +276,12 @@ def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[s
     S, H, dh = T // batch, cfg.n_head, cfg.head_dim
     _wgrad(dy, g, gr["fc2_w"], gr["fc2_b"])
     dg = torch.mm(dy, p["fc2_w"])
-    du = torch.ops.aten.gelu_backward(dg, u, approximate="tanh")
+    du = _gelu_bwd(dg, u, gr["fc1_b"])
     del dg
-    _wgrad(du, h2, gr["fc1_w"], gr["fc1_b"])
+    _wgrad(du, h2, gr["fc1_w"], None)
     dh2 = torch.mm(du, p["fc1_w"])
     del du
-    dx2 = _ln_bwd(dh2, x2, mean2, rstd2, p["ln2_w"], p["ln2_b"], gr["ln2_w"], gr["ln2_b"]).add_(dy)
+    dx2 = _ln_bwd(dh2, x2, mean2, rstd2, p["ln2_w"], p["ln2_b"], gr["ln2_w"], gr["ln2_b"], resid=dy)
     _wgrad(dx2, a, gr["proj_w"], gr["proj_b"])
     da = torch.mm(dx2, p["proj_w"])
     datt = da.view(batch, S, H, dh).transpose(1, 2)
@@ -237,7 +291,7 @@ def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[s
     dqkv = torch.cat([t.transpose(1, 2).reshape(T, d) for t in (dq, dk, dv)], dim=1)
     _wgrad(dqkv, h1, gr["qkv_w"], gr["qkv_b"])
     dh1 = torch.mm(dqkv, p["qkv_w"])
-    dx = _ln_bwd(dh1, x, mean1, rstd1, p["ln1_w"], p["ln1_b"], gr["ln1_w"], gr["ln1_b"]).add_(dx2)
+    dx = _ln_bwd(dh1, x, mean1, rstd1, p["ln1_w"], p["ln1_b"], gr["ln1_w"], gr["ln1_b"], resid=dx2)
     return dx
 
 
@@ -260,12 +314,14 @@ def embed_backward(dx: torch.Tensor, tokens: torch.Tensor, gr: Dict[str, torch.T
 
 def head_forward_backward(x: torch.Tensor, targets: torch.Tensor, p: Dict[str, torch.Tensor],
                           gr: Dict[str, torch.Tensor], cfg: GPTConfig, grad_scale: float, loss_sum: torch.Tensor,
-                          ce_fwd_bwd: Callable, chunk_tokens: int = 4096) -> torch.Tensor:
+                          ce_fwd_bwd: Callable, chunk_tokens: int = 4096,
+                          branch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Final layer norm, tied output projection and cross-entropy, forward and backward in
     one sweep over token chunks so the [T, vocab] logits never exist in full.  Adds the
-    summed token losses to ``loss_sum``; writes gr["wte"], gr["lnf_*"]; returns dx."""
+    summed token losses to ``loss_sum``; writes gr["wte"], gr["lnf_*"]; returns dx.  With
+    ``branch`` the input is ``x + branch`` (see ``layer_forward_deferred``)."""
     T, d = x.shape
-    hf, mean, rstd = _ln_fwd(x, p["lnf_w"], p["lnf_b"], cfg.ln_eps)
+    hf, mean, rstd, x = _ln_fwd(x, p["lnf_w"], p["lnf_b"], cfg.ln_eps, branch)
     wte = p["wte"]
     dhf = torch.empty_like(hf)
     gw = gr["wte"]

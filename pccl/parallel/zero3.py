@@ -95,7 +95,7 @@ class Zero3Engine:
     def __init__(self, cfg: GPTConfig, backend: Optional[TorchBackend] = None, optim: Optional[OptimConfig] = None,
                  device: Optional[torch.device] = None, seed: int = 1234, comm=None, group=None,
                  linear_fwd: Optional[Callable] = None, micro_batch: int = 1, fused_ag_gemm: bool = False,
-                 gather_ctas: int = 16):
+                 gather_ctas: int = 16, fused_gelu_gemm: bool = False):
         from .. import build_kernels
 
         self.C = build_kernels.load()
@@ -108,6 +108,8 @@ class Zero3Engine:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.comm = comm
         self.linear_fwd = linear_fwd or gpt._default_linear
+        # FC1 on the library's tcgen05 GEMM with bias and GELU in its epilogue (one kernel, two outputs)
+        self.fused_gelu_gemm = bool(fused_gelu_gemm)
         self.micro_batch = micro_batch
         self.step_count = 0
         self.launches = 0          # kernels of this library launched by the last step
@@ -282,6 +284,8 @@ class Zero3Engine:
         nxt = self._gather(1, 1, (0, 1) if self.fused_ag_gemm else ()) if L > 0 else None
         _wait(pending)
         x = gpt.embed_forward(tokens, self.pviews[0][0])
+        branch = None          # MLP output of the previous block; the next layer norm adds it to x in its own pass
+        gpt.fused_gelu_gemm = self.fused_gelu_gemm
         saved = []
         for li in range(1, L + 1):
             slot = li % 2
@@ -291,7 +295,7 @@ class Zero3Engine:
             skip = (0, 1) if self.fused_ag_gemm else ()
             nxt = self._gather(li + 1, 1 - slot, skip) if li < L else self._gather(0, 1 - slot)
             self._cur = (li, slot)
-            x, ctx = gpt.layer_forward(x, self.pviews[li][slot], cfg, B, self.linear_fwd)
+            x, branch, ctx = gpt.layer_forward_deferred(x, branch, self.pviews[li][slot], cfg, B, self.linear_fwd)
             self._cur = None
             saved.append(ctx)
         # ---- head: final norm, tied projection, loss; forward and backward together
@@ -299,7 +303,8 @@ class Zero3Engine:
         _wait(nxt)
         nxt = self._gather(L, 1 - head_slot) if L > 0 else None
         dx = gpt.head_forward_backward(x, targets, self.pviews[0][head_slot], self.gviews0, cfg, grad_scale,
-                                       self.loss_sum, self._ce)
+                                       self.loss_sum, self._ce, branch=branch)
+        del branch
         # ---- backward through the blocks
         for li in range(L, 0, -1):
             slot = li % 2
@@ -327,12 +332,18 @@ class Zero3Engine:
                 self.sq_norm if o.max_grad_norm > 0 else None)
         own = 2 + (1 if o.max_grad_norm > 0 else 0) + (T + 4095) // 4096
         self._gemm_errs.clear()
+        del gpt.gemm_errors[:-64]                     # keep the latest flags for check_errors
         self.launches = own + (self._native_launches() + gpt.native_launches - launches0)
         return self.loss_sum / T
 
     def check_errors(self) -> None:
         """Synchronise and raise if a kernel of the last steps gave up in a bounded wait."""
         torch.cuda.synchronize(self.device)
+        if gpt.gemm_errors:
+            codes = torch.stack([e.view(()) for e in gpt.gemm_errors]).tolist()
+            gpt.gemm_errors.clear()
+            if any(codes):
+                raise RuntimeError(f"a GEMM kernel gave up in a bounded wait (codes {sorted(set(c for c in codes if c))})")
         if self.comm is not None:
             self.comm.check(sync=False)
 

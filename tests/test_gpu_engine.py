@@ -218,3 +218,91 @@ def test_layer_norm_backward_matches_fp32_reference(shape):
     assert float((dx.float() - xr.grad).norm() / xr.grad.norm()) < 1e-2
     torch.testing.assert_close(dg.float(), gr.grad, rtol=2e-2, atol=2e-2 * float(gr.grad.abs().max()))
     torch.testing.assert_close(db.float(), br.grad, rtol=2e-2, atol=2e-2 * float(br.grad.abs().max()))
+    # with the gradient that flows around the norm added in the same pass
+    resid = torch.randn(T, d, device=DEV, generator=g).to(torch.bfloat16)
+    dx2 = pccl._C.ln_bwd(dy, x, mean.view(-1), rstd.view(-1), gamma, dg, db, resid)
+    want = xr.grad + resid.float()
+    assert float((dx2.float() - want).norm() / want.norm()) < 1e-2
+    torch.testing.assert_close(dg.float(), gr.grad, rtol=2e-2, atol=2e-2 * float(gr.grad.abs().max()))
+
+
+@pytest.mark.parametrize("with_branch", [False, True])
+@pytest.mark.parametrize("shape", [(8192, 2048), (333, 1024), (2048, 4096), (1, 2048)])
+def test_layer_norm_forward_matches_fp32_reference(shape, with_branch):
+    import pccl
+
+    T, d = shape
+    g = torch.Generator(device=DEV).manual_seed(7 * T + d)
+    x = (torch.randn(T, d, device=DEV, generator=g) * 2 + 0.5).to(torch.bfloat16)
+    branch = torch.randn(T, d, device=DEV, generator=g).to(torch.bfloat16) if with_branch else None
+    gamma = (torch.randn(d, device=DEV, generator=g) * 0.2 + 1).to(torch.bfloat16)
+    beta = (torch.randn(d, device=DEV, generator=g) * 0.1).to(torch.bfloat16)
+    xs = (x.float() + branch.float()).to(torch.bfloat16) if with_branch else x      # the sum as bf16 stores it
+    ref = torch.nn.functional.layer_norm(xs.float(), (d,), gamma.float(), beta.float(), 1e-5)
+    mu = xs.float().mean(1)
+    rs = (xs.float().var(1, unbiased=False) + 1e-5).rsqrt()
+    y, mean, rstd = pccl._C.ln_fwd(x, branch, gamma, beta, 1e-5)
+    if with_branch:
+        assert torch.equal(branch, xs), "the residual sum must land in the branch buffer, rounded once"
+    assert float((y.float() - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+    assert float((y.float() - ref).norm() / ref.norm()) < 4e-3
+    torch.testing.assert_close(mean, mu, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(rstd, rs, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(4096, 8192), (1000, 4096), (37, 8), (5, 72)])
+def test_gelu_forward_and_backward_with_bias_gradient(shape):
+    import pccl
+
+    T, N = shape
+    g = torch.Generator(device=DEV).manual_seed(T * 3 + N)
+    u = (torch.randn(T, N, device=DEV, generator=g) * 2).to(torch.bfloat16)
+    u[0, :8] = torch.tensor([-30., -8., -3., -0.5, 0., 0.5, 8., 30.], device=DEV).to(torch.bfloat16)   # tails and zero
+    dg = torch.randn(T, N, device=DEV, generator=g).to(torch.bfloat16)
+    ur = u.float().requires_grad_()
+    ref = torch.nn.functional.gelu(ur, approximate="tanh")
+    ref.backward(dg.float())
+    y = pccl._C.gelu(u)
+    assert torch.isfinite(y.float()).all()
+    assert float((y.float() - ref.detach()).abs().max()) <= 1e-2 * float(ref.abs().max()) + 1e-3
+    assert float((y.float() - ref.detach()).norm() / ref.norm()) < 4e-3
+    gb = torch.empty(N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):                                  # twice: the tile counters must come back to zero
+        gb.zero_()
+        du = pccl._C.gelu_bwd_col_sum(dg, u, gb)
+        assert torch.isfinite(du.float()).all()
+        assert float((du.float() - ur.grad).norm() / ur.grad.norm()) < 4e-3
+        want = du.float().sum(0)
+        torch.testing.assert_close(gb.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) + 1e-3)
+
+
+@pytest.mark.parametrize("fused_gelu_gemm", [False, True])
+def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm):
+    """A two-block model wide enough (d = 1024) for the fused add+layer-norm, layer-norm backward
+    with residual, GELU and GELU-backward kernels, with FC1 optionally on the tcgen05 GEMM whose
+    epilogue applies the GELU: loss and every gradient against torch autograd in fp32."""
+    from pccl.models import gpt
+    from pccl.models.gpt import GPTConfig
+    from pccl.parallel.backend import TorchBackend
+    from pccl.parallel.zero3 import OptimConfig, Zero3Engine
+    from pccl.utils.env import init_distributed
+
+    init_distributed()
+    cfg = GPTConfig(2, 1024, 8, 4096, vocab=2048, seq_len=128, name="gpt-test-1024")
+    engine = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=0.0, weight_decay=0.0), fused_gelu_gemm=fused_gelu_gemm)
+    g = torch.Generator().manual_seed(11)
+    toks = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=g).to(DEV)
+    tokens, targets = toks[:, :-1].contiguous(), toks[:, 1:].contiguous()
+    ref_loss, ref_params = _autograd_reference(cfg, engine, tokens, targets)
+    before = gpt.native_launches
+    loss = engine.train_step(tokens, targets)
+    engine.check_errors()
+    # per block: 2 ln_fwd, gelu or gemm_gelu, gelu_bwd, 3 col_sum, 2 x (ln_bwd + finalize); head: ln_fwd, ln_bwd + finalize
+    assert gpt.native_launches - before == cfg.n_layer * 11 + 3
+    torch.testing.assert_close(loss[0], ref_loss, rtol=2e-2, atol=2e-2)
+    for ui, u in enumerate(engine.units):
+        got = gpt.views(u, engine.grad_shard[engine.shard_off[ui]:engine.shard_off[ui + 1]])
+        for name, ref in ref_params[ui].items():
+            gr, rf = got[name].float(), ref.grad
+            err = (gr - rf).norm() / (rf.norm() + 1e-12)
+            assert err < 6e-2, f"unit {u.name} grad {name}: relative error {float(err):.3e}"

@@ -39,6 +39,27 @@ def test_gemm_matches_fp32_reference(shape, two_cta):
     check_close(y2, A.float() @ W.float().t(), K)
 
 
+@pytest.mark.parametrize("two_cta", [False, True], ids=["one_sm", "cta_pair"])
+@pytest.mark.parametrize("shape", [(256, 512, 128), (1000, 520, 328), (2048, 4096, 1024)])
+def test_gemm_with_gelu_epilogue(shape, two_cta):
+    """One kernel, two outputs: the pre-activation (kept for the backward pass) and its GELU."""
+    import pccl
+
+    M, N, K = shape
+    A, W = rnd((M, K), 1), rnd((N, K), 2, 0.08)
+    bias = rnd((N,), 3)
+    u, g, err = pccl._C.gemm_gelu(A, W, bias, two_cta)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    ref_u = A.float() @ W.float().t() + bias.float()
+    check_close(u, ref_u, K)
+    y_plain, _ = pccl._C.gemm(A, W, bias, None, two_cta)
+    assert torch.equal(u, y_plain), "the pre-activation must not depend on the second output"
+    ref_g = torch.nn.functional.gelu(u.float(), approximate="tanh")      # the activation reads the stored bf16 value
+    assert float((g.float() - ref_g).abs().max()) <= 1e-2 * float(ref_g.abs().max()) + 1e-3
+    assert float((g.float() - ref_g).norm() / ref_g.norm()) < 4e-3
+
+
 def test_linear_wrapper_and_identity():
     from pccl.ops.gemm import linear
 
