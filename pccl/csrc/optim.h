@@ -33,6 +33,11 @@ cudaError_t launch_col_sum(const void* X, int64_t T, int N, void* out, float* pa
 cudaError_t launch_gelu_bwd_col_sum(const void* dg, const void* u, void* du, int64_t T, int N, void* out, float* partial,
                                     int* counters, int R, cudaStream_t s);
 
+// cat = [a | b | c] (three [T, N/3] bf16 matrices side by side, N % 24 == 0) and out[c] = column
+// sums of cat, in one pass.  Scratch as for launch_col_sum.
+cudaError_t launch_cat3_col_sum(const void* a, const void* b, const void* c, void* cat, int64_t T, int N, void* out,
+                                float* partial, int* counters, int R, cudaStream_t s);
+
 // out = gelu(in), tanh form, bf16, n % 8 == 0, both 16-byte aligned.
 cudaError_t launch_gelu_fwd(const void* in, void* out, int64_t n, cudaStream_t s);
 
@@ -42,10 +47,11 @@ cudaError_t launch_ln_fwd(const void* x, void* branch, const void* gamma, const 
                           int64_t T, int d, float eps, cudaStream_t s);
 
 // Layer-norm backward for bf16 activations with d in {1024, 2048, 4096}: writes dx (+ resid when
-// given), dgamma, dbeta.  pgamma / pbeta: ln_bwd_blocks() * d floats of scratch each.
+// given), dgamma, dbeta and, when dx_col_sum is given, the column sums of the stored dx.
+// scratch: 3 * ln_bwd_blocks() * d floats.
 int ln_bwd_blocks();
 cudaError_t launch_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma, void* dx,
-                          const void* resid, void* dgamma, void* dbeta, float* pgamma, float* pbeta, int64_t T, int d,
+                          const void* resid, void* dgamma, void* dbeta, void* dx_col_sum, float* scratch, int64_t T, int d,
                           cudaStream_t s);
 
 }  // namespace pccl

@@ -135,6 +135,28 @@ at::Tensor gelu_bwd_col_sum(const at::Tensor& dg, const at::Tensor& u, at::Tenso
   return du;
 }
 
+// [a | b | c] and its column sums in one pass (the packed q/k/v gradient and the QKV bias gradient).
+at::Tensor cat3_col_sum(const at::Tensor& a, const at::Tensor& b, const at::Tensor& c, at::Tensor& bias_grad) {
+  for (const at::Tensor* t : {&a, &b, &c})
+    TORCH_CHECK(t->is_cuda() && t->dim() == 2 && t->scalar_type() == at::kBFloat16 && t->is_contiguous() &&
+                    t->sizes() == a.sizes() && t->device() == a.device() && ((uintptr_t)t->data_ptr()) % 16 == 0,
+                "a, b, c must be contiguous 2-D bfloat16 CUDA tensors of one shape, 16-byte aligned");
+  const int64_t T = a.size(0);
+  const int N = 3 * (int)a.size(1);
+  check_flat(bias_grad, "bias_grad", at::kBFloat16);
+  TORCH_CHECK(a.size(1) % 8 == 0 && bias_grad.numel() == N, "columns must be a multiple of 8; bias_grad holds 3x columns");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int dev = a.get_device();
+  at::Tensor cat = at::empty({T, N}, a.options());
+  const int R = col_sum_row_splits(T, N);
+  TORCH_CHECK((int64_t)R * N <= (int64_t)64 * 8192, "too many columns for the column-sum scratch");
+  at::Tensor& part = scratch(dev, (int64_t)R * N);
+  at::Tensor& cnt = counters(dev, (N + 63) / 64);
+  PCCL_CUDA(launch_cat3_col_sum(a.data_ptr(), b.data_ptr(), c.data_ptr(), cat.data_ptr(), T, N, bias_grad.data_ptr(),
+                                part.data_ptr<float>(), cnt.data_ptr<int>(), R, at::cuda::getCurrentCUDAStream().stream()));
+  return cat;
+}
+
 at::Tensor gelu(const at::Tensor& u) {
   TORCH_CHECK(u.is_cuda() && u.scalar_type() == at::kBFloat16 && u.is_contiguous(), "u must be a contiguous bfloat16 CUDA tensor");
   TORCH_CHECK(u.numel() % 8 == 0 && ((uintptr_t)u.data_ptr()) % 16 == 0, "numel % 8 == 0 and 16-byte alignment required");
@@ -171,7 +193,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> ln_fwd(const at::Tensor& x, std::
 }
 
 at::Tensor ln_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& mean, const at::Tensor& rstd,
-                  const at::Tensor& gamma, at::Tensor& dgamma, at::Tensor& dbeta, std::optional<at::Tensor> resid) {
+                  const at::Tensor& gamma, at::Tensor& dgamma, at::Tensor& dbeta, std::optional<at::Tensor> resid,
+                  std::optional<at::Tensor> dx_col_sum) {
   TORCH_CHECK(dy.is_cuda() && dy.dim() == 2 && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous(), "dy: 2-D bf16");
   TORCH_CHECK(x.sizes() == dy.sizes() && x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "x must match dy");
   const int64_t T = dy.size(0), d = dy.size(1);
@@ -190,14 +213,20 @@ at::Tensor ln_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& m
                 "resid must match dy");
     rptr = resid->data_ptr();
   }
+  void* sptr = nullptr;
+  if (dx_col_sum.has_value()) {
+    check_flat(*dx_col_sum, "dx_col_sum", at::kBFloat16);
+    TORCH_CHECK(dx_col_sum->numel() == d && dx_col_sum->device() == dy.device(), "dx_col_sum must hold d elements");
+    sptr = dx_col_sum->data_ptr();
+  }
   c10::cuda::CUDAGuard guard(dy.device());
   const int dev = dy.get_device();
   at::Tensor dx = at::empty_like(dy);
   const int64_t part = (int64_t)ln_bwd_blocks() * d;
-  at::Tensor& sc = scratch(dev, 2 * part + (int64_t)64 * 8192);
+  at::Tensor& sc = scratch(dev, 3 * part + (int64_t)64 * 8192);
   float* pg = sc.data_ptr<float>() + (int64_t)64 * 8192;     // the front of the buffer belongs to col_sum
   PCCL_CUDA(launch_ln_bwd(dy.data_ptr(), x.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr(),
-                          dx.data_ptr(), rptr, dgamma.data_ptr(), dbeta.data_ptr(), pg, pg + part, T, (int)d,
+                          dx.data_ptr(), rptr, dgamma.data_ptr(), dbeta.data_ptr(), sptr, pg, T, (int)d,
                           at::cuda::getCurrentCUDAStream().stream()));
   return dx;
 }
@@ -207,11 +236,12 @@ at::Tensor ln_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& m
 void bind_optim(py::module_& m) {
   m.def("col_sum", &col_sum, "out[c] = sum_r x[r, c] (bf16 in/out, fp32 accumulation)");
   m.def("ln_bwd", &ln_bwd, py::arg("dy"), py::arg("x"), py::arg("mean"), py::arg("rstd"), py::arg("gamma"), py::arg("dgamma"),
-        py::arg("dbeta"), py::arg("resid") = py::none(),
-        "layer-norm backward: returns dx (+ resid), writes dgamma and dbeta");
+        py::arg("dbeta"), py::arg("resid") = py::none(), py::arg("dx_col_sum") = py::none(),
+        "layer-norm backward: returns dx (+ resid), writes dgamma, dbeta and optionally the column sums of dx");
   m.def("ln_fwd", &ln_fwd, py::arg("x"), py::arg("branch"), py::arg("gamma"), py::arg("beta"), py::arg("eps"),
         "layer norm of x (+ branch, summed in place into branch): returns (y, mean, rstd)");
   m.def("gelu", &gelu, "tanh-form GELU, bf16");
+  m.def("cat3_col_sum", &cat3_col_sum, "returns [a | b | c]; bias_grad = its column sums");
   m.def("gelu_bwd_col_sum", &gelu_bwd_col_sum, "du = dg * gelu'(u); bias_grad = column sums of du");
   m.def("ln_bwd_supported", &ln_bwd_supported);
   m.def("sq_norm", &sq_norm, "out += sum(x*x)");

@@ -44,28 +44,32 @@ __device__ __forceinline__ float round_bf16(float f) { return __bfloat162float(_
 // GELU form: X is the gradient of the GELU's output and U its input; the kernel writes
 // DU = X * gelu'(U) and sums the columns of DU (as rounded to bf16), the bias gradient of
 // the linear layer in front of the GELU.
+// Concatenating form: the columns are those of three [T, N/3] matrices side by side (the
+// gradients of q, k and v); the kernel writes the [T, N] concatenation to DU while it sums.
 constexpr int kColTile = 512, kRowLanes = 4;
+enum ColMode { kColSum = 0, kColGelu = 1, kColCat3 = 2 };
 
-template <bool GELU>
+template <int MODE>
 __device__ __forceinline__ void col_item(const uint4& q, const uint4& uq, __nv_bfloat16* DU, int64_t off, float* acc) {
   float f[8];
   unpack8(q, f);
-  if (GELU) {
+  if (MODE == kColGelu) {
     float u[8];
     unpack8(uq, u);
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] = round_bf16(f[e] * gelu_tanh_grad(u[e]));
     *reinterpret_cast<uint4*>(DU + off) = pack8(f);
   }
+  if (MODE == kColCat3) *reinterpret_cast<uint4*>(DU + off) = q;
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] += f[e];
 }
 
-template <bool GELU>
+template <int MODE>
 __global__ void __launch_bounds__(256) col_sum_kernel(const __nv_bfloat16* __restrict__ X, int64_t T, int N,
                                                       __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
                                                       int* __restrict__ counters, const __nv_bfloat16* __restrict__ U,
-                                                      __nv_bfloat16* __restrict__ DU) {
+                                                      __nv_bfloat16* __restrict__ DU, const __nv_bfloat16* __restrict__ X2) {
   __shared__ __align__(16) float red[kRowLanes][kColTile];
   __shared__ int s_last;
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
@@ -79,23 +83,29 @@ __global__ void __launch_bounds__(256) col_sum_kernel(const __nv_bfloat16* __res
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
   if (col < N) {
+    // where this thread's 8 columns come from: X itself, or one of the three sources
+    const __nv_bfloat16* src = X + col;
+    int64_t ld = N;
+    if (MODE == kColCat3) {
+      const int w = N / 3, which = col / w;
+      src = (which == 0 ? X : which == 1 ? U : X2) + (col - which * w);
+      ld = w;
+    }
     int64_t r = r0 + ty;
     for (; r + 3 * kRowLanes < r1; r += 4 * kRowLanes) {
       uint4 q[4], uq[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int64_t off = (r + k * kRowLanes) * N + col;
-        q[k] = *reinterpret_cast<const uint4*>(X + off);
-        uq[k] = GELU ? *reinterpret_cast<const uint4*>(U + off) : make_uint4(0, 0, 0, 0);
+        q[k] = *reinterpret_cast<const uint4*>(src + (r + k * kRowLanes) * ld);
+        uq[k] = MODE == kColGelu ? *reinterpret_cast<const uint4*>(U + (r + k * kRowLanes) * N + col) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
-      for (int k = 0; k < 4; ++k) col_item<GELU>(q[k], uq[k], DU, (r + k * kRowLanes) * N + col, acc);
+      for (int k = 0; k < 4; ++k) col_item<MODE>(q[k], uq[k], DU, (r + k * kRowLanes) * N + col, acc);
     }
     for (; r < r1; r += kRowLanes) {
-      const int64_t off = r * N + col;
-      const uint4 q = *reinterpret_cast<const uint4*>(X + off);
-      const uint4 uq = GELU ? *reinterpret_cast<const uint4*>(U + off) : make_uint4(0, 0, 0, 0);
-      col_item<GELU>(q, uq, DU, off, acc);
+      const uint4 q = *reinterpret_cast<const uint4*>(src + r * ld);
+      const uint4 uq = MODE == kColGelu ? *reinterpret_cast<const uint4*>(U + r * N + col) : make_uint4(0, 0, 0, 0);
+      col_item<MODE>(q, uq, DU, r * N + col, acc);
     }
   }
   *reinterpret_cast<float4*>(&red[ty][tx * 8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -148,159 +158,185 @@ __global__ void __launch_bounds__(256) col_sum_kernel(const __nv_bfloat16* __res
 // ---------------------------------------------------------------- layer-norm backward
 // One pass over dy and x:  dx = rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dy * gamma,
 // and per-block partial sums of dgamma = sum_r dy * xhat, dbeta = sum_r dy.
-// 128 threads work on one row (EPT = d / 128 elements each, in 16-byte vectors), NG rows per
-// block iteration; the row groups add their dgamma/dbeta sums through shared memory, so a
-// block leaves one partial row, and a second small kernel adds the blocks' partials.  With
-// `resid` the gradient that flows around the layer norm (the residual connection) is added
-// to dx in the same pass.
-template <int EPT, int NG>
-__global__ void __launch_bounds__(128 * NG, 1)
+//
+// 128 threads work on one row (EPT = d / 128 elements each, in 16-byte vectors).  A block has
+// two such row groups and each group takes RB rows per iteration: all their loads (dy, x and the
+// residual gradient, kept packed as bf16) are issued before the first use, so a block keeps
+// 2 * RB rows in flight, and the RB row reductions share one pair of block barriers.
+// With `resid` the gradient that flows around the layer norm (the residual connection) is added
+// to dx in the same pass (in fp32, before the one rounding); with `pdx` the kernel also sums the columns of dx (the
+// bias gradient of the linear layer whose output gradient dx is).  The two groups add their
+// column sums through shared memory, so a block leaves one partial row per array, and a second
+// small kernel adds the blocks' partials.
+template <int EPT>
+__device__ __forceinline__ void ln_bwd_combine(const float* acc, float* comb, float* out_row, int rg, int t) {
+  constexpr int NV = EPT / 8;
+  if (rg == 0) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      float4* c = reinterpret_cast<float4*>(comb + (t + 128 * k) * 8);
+      c[0] = make_float4(acc[8 * k], acc[8 * k + 1], acc[8 * k + 2], acc[8 * k + 3]);
+      c[1] = make_float4(acc[8 * k + 4], acc[8 * k + 5], acc[8 * k + 6], acc[8 * k + 7]);
+    }
+  }
+  __syncthreads();
+  if (rg == 1) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const float4* c = reinterpret_cast<const float4*>(comb + (t + 128 * k) * 8);
+      const float4 a0 = c[0], a1 = c[1];
+      float4* o = reinterpret_cast<float4*>(out_row + (t + 128 * k) * 8);
+      o[0] = make_float4(a0.x + acc[8 * k], a0.y + acc[8 * k + 1], a0.z + acc[8 * k + 2], a0.w + acc[8 * k + 3]);
+      o[1] = make_float4(a1.x + acc[8 * k + 4], a1.y + acc[8 * k + 5], a1.z + acc[8 * k + 6], a1.w + acc[8 * k + 7]);
+    }
+  }
+  __syncthreads();
+}
+
+template <int EPT, int RB>
+__global__ void __launch_bounds__(256, 1)
     ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
                   const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ gamma,
                   const __nv_bfloat16* __restrict__ resid, __nv_bfloat16* __restrict__ dx, float* __restrict__ pgamma,
-                  float* __restrict__ pbeta, int64_t T, int d) {
+                  float* __restrict__ pbeta, float* __restrict__ pdx, int64_t T, int d) {
   constexpr int NV = EPT / 8;
-  __shared__ float red[NG][4][2];
-  __shared__ __align__(16) float comb[2][128 * EPT];
+  __shared__ float red[2][RB][4][2];
+  __shared__ __align__(16) float comb[128 * EPT];
   const int rg = threadIdx.x >> 7, t = threadIdx.x & 127, warp_in_rg = t >> 5, lane = t & 31;
-  float gam[EPT], dgam[EPT], dbet[EPT];
+  uint4 pgam[NV];
+  float dgam[EPT], dbet[EPT], dxs[EPT];
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
-    unpack8(*reinterpret_cast<const uint4*>(gamma + (t + 128 * k) * 8), gam + 8 * k);
+    pgam[k] = *reinterpret_cast<const uint4*>(gamma + (t + 128 * k) * 8);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) dgam[8 * k + e] = dbet[8 * k + e] = 0.f;
+    for (int e = 0; e < 8; ++e) dgam[8 * k + e] = dbet[8 * k + e] = dxs[8 * k + e] = 0.f;
   }
   const float inv_d = 1.0f / (float)d;
-  const int64_t iters = (T + NG * (int64_t)gridDim.x - 1) / (NG * (int64_t)gridDim.x);
-  for (int64_t it = 0; it < iters; ++it) {
-    const int64_t r = (it * gridDim.x + blockIdx.x) * NG + rg;
-    const bool live = r < T;
-    float g[EPT], xh[EPT];
-    float s1 = 0.f, s2 = 0.f;
-    float rs = 0.f;
-    if (live) {
-      const float mu = mean[r];
-      rs = rstd[r];
+  const int64_t step = 2 * RB * (int64_t)gridDim.x;
+  for (int64_t base = (int64_t)blockIdx.x * 2 * RB; base < T; base += step) {
+    uint4 pdy[RB][NV], px[RB][NV], pr[RB][NV];
+    float mu[RB], rs[RB];
+    // ---- all loads of this group's rows
+#pragma unroll
+    for (int j = 0; j < RB; ++j) {
+      const int64_t r = base + rg * RB + j;
+      mu[j] = 0.f;
+      rs[j] = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) pdy[j][k] = px[j][k] = pr[j][k] = make_uint4(0, 0, 0, 0);
+      if (r < T) {
+        mu[j] = mean[r];
+        rs[j] = rstd[r];
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          const int64_t off = r * d + (t + 128 * k) * 8;
+          pdy[j][k] = *reinterpret_cast<const uint4*>(dy + off);
+          px[j][k] = *reinterpret_cast<const uint4*>(x + off);
+          if (resid != nullptr) pr[j][k] = *reinterpret_cast<const uint4*>(resid + off);
+        }
+      }
+    }
+    // ---- row sums and the weight/bias gradient sums (rows past the end hold zeros)
+#pragma unroll
+    for (int j = 0; j < RB; ++j) {
+      float s1 = 0.f, s2 = 0.f;
+      const float nmr = -mu[j] * rs[j];
 #pragma unroll
       for (int k = 0; k < NV; ++k) {
-        float a[8], b[8];
-        unpack8(*reinterpret_cast<const uint4*>(dy + r * d + (t + 128 * k) * 8), a);
-        unpack8(*reinterpret_cast<const uint4*>(x + r * d + (t + 128 * k) * 8), b);
+        float a[8], b[8], g[8];
+        unpack8(pdy[j][k], a);
+        unpack8(px[j][k], b);
+        unpack8(pgam[k], g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const float xhat = (b[e] - mu) * rs;
-          const float gg = a[e] * gam[8 * k + e];
-          xh[8 * k + e] = xhat;
-          g[8 * k + e] = gg;
+          const float xhat = fmaf(b[e], rs[j], nmr);
+          const float gg = a[e] * g[e];
           s1 += gg;
-          s2 += gg * xhat;
-          dgam[8 * k + e] += a[e] * xhat;
+          s2 = fmaf(gg, xhat, s2);
+          dgam[8 * k + e] = fmaf(a[e], xhat, dgam[8 * k + e]);
           dbet[8 * k + e] += a[e];
         }
       }
-    }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-    }
-    if (lane == 0) {
-      red[rg][warp_in_rg][0] = s1;
-      red[rg][warp_in_rg][1] = s2;
-    }
-    __syncthreads();
-    s1 = red[rg][0][0] + red[rg][1][0] + red[rg][2][0] + red[rg][3][0];
-    s2 = red[rg][0][1] + red[rg][1][1] + red[rg][2][1] + red[rg][3][1];
-    __syncthreads();
-    if (live) {
-      const float m1 = s1 * inv_d, m2 = s2 * inv_d;
-#pragma unroll
-      for (int k = 0; k < NV; ++k) {
-        float o8[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) o8[e] = (g[8 * k + e] - m1 - xh[8 * k + e] * m2) * rs;
-        if (resid != nullptr) {
-          float q8[8];
-          unpack8(*reinterpret_cast<const uint4*>(resid + r * d + (t + 128 * k) * 8), q8);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o8[e] = round_bf16(o8[e]) + q8[e];     // same roundings as a separate add
-        }
-        *reinterpret_cast<uint4*>(dx + r * d + (t + 128 * k) * 8) = pack8(o8);
+      for (int o = 16; o > 0; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+      }
+      if (lane == 0) {
+        red[rg][j][warp_in_rg][0] = s1;
+        red[rg][j][warp_in_rg][1] = s2;
       }
     }
-  }
-  // the row groups take turns adding their column sums into shared memory
-#pragma unroll 1
-  for (int gi = 0; gi < NG; ++gi) {
-    if (rg == gi) {
+    __syncthreads();
+    // ---- dx
 #pragma unroll
-      for (int k = 0; k < NV; ++k) {
-        const int c = (t + 128 * k) * 8;
-        float4* cg = reinterpret_cast<float4*>(&comb[0][c]);
-        float4* cb = reinterpret_cast<float4*>(&comb[1][c]);
-        float4 g0 = make_float4(dgam[8 * k], dgam[8 * k + 1], dgam[8 * k + 2], dgam[8 * k + 3]);
-        float4 g1 = make_float4(dgam[8 * k + 4], dgam[8 * k + 5], dgam[8 * k + 6], dgam[8 * k + 7]);
-        float4 b0 = make_float4(dbet[8 * k], dbet[8 * k + 1], dbet[8 * k + 2], dbet[8 * k + 3]);
-        float4 b1 = make_float4(dbet[8 * k + 4], dbet[8 * k + 5], dbet[8 * k + 6], dbet[8 * k + 7]);
-        if (gi > 0) {
-          const float4 pg0 = cg[0], pg1 = cg[1], pb0 = cb[0], pb1 = cb[1];
-          g0.x += pg0.x, g0.y += pg0.y, g0.z += pg0.z, g0.w += pg0.w;
-          g1.x += pg1.x, g1.y += pg1.y, g1.z += pg1.z, g1.w += pg1.w;
-          b0.x += pb0.x, b0.y += pb0.y, b0.z += pb0.z, b0.w += pb0.w;
-          b1.x += pb1.x, b1.y += pb1.y, b1.z += pb1.z, b1.w += pb1.w;
+    for (int j = 0; j < RB; ++j) {
+      const int64_t r = base + rg * RB + j;
+      if (r < T) {
+        const float m1 = (red[rg][j][0][0] + red[rg][j][1][0] + red[rg][j][2][0] + red[rg][j][3][0]) * inv_d;
+        const float m2 = (red[rg][j][0][1] + red[rg][j][1][1] + red[rg][j][2][1] + red[rg][j][3][1]) * inv_d;
+        // dx = rs * (dy * gamma - m1 - xhat * m2) = dy * (gamma * rs) - x * c2 + c0
+        const float c2 = rs[j] * rs[j] * m2;
+        const float c0 = fmaf(mu[j], c2, -m1 * rs[j]);
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          float a[8], b[8], g[8], o8[8];
+          unpack8(pdy[j][k], a);
+          unpack8(px[j][k], b);
+          unpack8(pgam[k], g);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o8[e] = fmaf(a[e], g[e] * rs[j], fmaf(b[e], -c2, c0));
+          if (resid != nullptr) {
+            float q8[8];
+            unpack8(pr[j][k], q8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o8[e] += q8[e];                        // one rounding, at the store
+          }
+          *reinterpret_cast<uint4*>(dx + r * d + (t + 128 * k) * 8) = pack8(o8);
+          if (pdx != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dxs[8 * k + e] += o8[e];
+          }
         }
-        cg[0] = g0, cg[1] = g1, cb[0] = b0, cb[1] = b1;
       }
     }
     __syncthreads();
   }
-  float4* pg = reinterpret_cast<float4*>(pgamma + (int64_t)blockIdx.x * d);
-  float4* pb = reinterpret_cast<float4*>(pbeta + (int64_t)blockIdx.x * d);
-  for (int i = threadIdx.x; i < d / 4; i += 128 * NG) {
-    pg[i] = reinterpret_cast<const float4*>(comb[0])[i];
-    pb[i] = reinterpret_cast<const float4*>(comb[1])[i];
-  }
+  ln_bwd_combine<EPT>(dgam, comb, pgamma + (int64_t)blockIdx.x * d, rg, t);
+  ln_bwd_combine<EPT>(dbet, comb, pbeta + (int64_t)blockIdx.x * d, rg, t);
+  if (pdx != nullptr) ln_bwd_combine<EPT>(dxs, comb, pdx + (int64_t)blockIdx.x * d, rg, t);
 }
 
-// Adds the per-block partial sums: a block owns 32 columns, its 8 warps split the partials.
-__global__ void __launch_bounds__(256) ln_bwd_finalize_kernel(const float* __restrict__ pgamma, const float* __restrict__ pbeta,
-                                                              int nparts, int d, __nv_bfloat16* __restrict__ dgamma,
-                                                              __nv_bfloat16* __restrict__ dbeta) {
-  __shared__ float sa[8][33], sb[8][33];
+// Adds the per-block partial sums of up to three arrays (blockIdx.y picks the array): a block
+// owns 32 columns, its 8 warps split the partials.
+struct LnBwdFinalizeArgs {
+  const float* part[3];
+  __nv_bfloat16* out[3];
+};
+
+__global__ void __launch_bounds__(256) ln_bwd_finalize_kernel(LnBwdFinalizeArgs f, int nparts, int d) {
+  __shared__ float sa[8][33];
+  const float* __restrict__ part = f.part[blockIdx.y];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + lane;
-  float a = 0.f, b = 0.f;
+  float a = 0.f;
   if (c < d) {
     int p = w;
-    for (; p + 24 < nparts; p += 32) {              // four rows of each array in flight
-      float va[4], vb[4];
+    for (; p + 56 < nparts; p += 64) {              // eight rows in flight
+      float va[8];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        va[k] = __ldcg(pgamma + (int64_t)(p + 8 * k) * d + c);
-        vb[k] = __ldcg(pbeta + (int64_t)(p + 8 * k) * d + c);
-      }
+      for (int k = 0; k < 8; ++k) va[k] = __ldcg(part + (int64_t)(p + 8 * k) * d + c);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        a += va[k];
-        b += vb[k];
-      }
+      for (int k = 0; k < 8; ++k) a += va[k];
     }
-    for (; p < nparts; p += 8) {
-      a += __ldcg(pgamma + (int64_t)p * d + c);
-      b += __ldcg(pbeta + (int64_t)p * d + c);
-    }
+    for (; p < nparts; p += 8) a += __ldcg(part + (int64_t)p * d + c);
   }
   sa[w][lane] = a;
-  sb[w][lane] = b;
   __syncthreads();
   if (w == 0 && c < d) {
 #pragma unroll
-    for (int k = 1; k < 8; ++k) {
-      a += sa[k][lane];
-      b += sb[k][lane];
-    }
-    dgamma[c] = __float2bfloat16_rn(a);
-    dbeta[c] = __float2bfloat16_rn(b);
+    for (int k = 1; k < 8; ++k) a += sa[k][lane];
+    f.out[blockIdx.y][c] = __float2bfloat16_rn(a);
   }
 }
 
@@ -413,8 +449,8 @@ cudaError_t launch_col_sum(const void* X, int64_t T, int N, void* out, float* pa
   if (T <= 0 || N <= 0) return cudaSuccess;
   if (N % 8 != 0) return cudaErrorInvalidValue;
   dim3 grid((N + kColTile - 1) / kColTile, R);
-  col_sum_kernel<false><<<grid, 256, 0, s>>>((const __nv_bfloat16*)X, T, N, (__nv_bfloat16*)out, partial, counters, nullptr,
-                                             nullptr);
+  col_sum_kernel<kColSum><<<grid, 256, 0, s>>>((const __nv_bfloat16*)X, T, N, (__nv_bfloat16*)out, partial, counters, nullptr,
+                                               nullptr, nullptr);
   return cudaGetLastError();
 }
 
@@ -423,8 +459,18 @@ cudaError_t launch_gelu_bwd_col_sum(const void* dg, const void* u, void* du, int
   if (T <= 0 || N <= 0) return cudaSuccess;
   if (N % 8 != 0) return cudaErrorInvalidValue;
   dim3 grid((N + kColTile - 1) / kColTile, R);
-  col_sum_kernel<true><<<grid, 256, 0, s>>>((const __nv_bfloat16*)dg, T, N, (__nv_bfloat16*)out, partial, counters,
-                                            (const __nv_bfloat16*)u, (__nv_bfloat16*)du);
+  col_sum_kernel<kColGelu><<<grid, 256, 0, s>>>((const __nv_bfloat16*)dg, T, N, (__nv_bfloat16*)out, partial, counters,
+                                                (const __nv_bfloat16*)u, (__nv_bfloat16*)du, nullptr);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cat3_col_sum(const void* a, const void* b, const void* c, void* cat, int64_t T, int N, void* out,
+                                float* partial, int* counters, int R, cudaStream_t s) {
+  if (T <= 0 || N <= 0) return cudaSuccess;
+  if (N % 24 != 0) return cudaErrorInvalidValue;          // three sources of a multiple of 8 columns each
+  dim3 grid((N + kColTile - 1) / kColTile, R);
+  col_sum_kernel<kColCat3><<<grid, 256, 0, s>>>((const __nv_bfloat16*)a, T, N, (__nv_bfloat16*)out, partial, counters,
+                                                (const __nv_bfloat16*)b, (__nv_bfloat16*)cat, (const __nv_bfloat16*)c);
   return cudaGetLastError();
 }
 
@@ -456,30 +502,35 @@ cudaError_t launch_ln_fwd(const void* x, void* branch, const void* gamma, const 
   return cudaGetLastError();
 }
 
-int ln_bwd_blocks() { return 148; }      // one block per SM; each leaves one partial row
+int ln_bwd_blocks() { return 148; }      // one block per SM; each leaves one partial row per array
 
 cudaError_t launch_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma, void* dx,
-                          const void* resid, void* dgamma, void* dbeta, float* pgamma, float* pbeta, int64_t T, int d,
+                          const void* resid, void* dgamma, void* dbeta, void* dx_col_sum, float* scratch, int64_t T, int d,
                           cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
-  const int ng = d <= 2048 ? 4 : 2;          // rows per block iteration
+  const int rb = d <= 2048 ? 4 : 1;          // rows per group per iteration (register budget)
   int blocks = ln_bwd_blocks();
-  if ((int64_t)blocks * ng > T) blocks = (int)((T + ng - 1) / ng);
+  if ((int64_t)blocks * 2 * rb > T) blocks = (int)((T + 2 * rb - 1) / (2 * rb));
   auto* DY = (const __nv_bfloat16*)dy;
   auto* X = (const __nv_bfloat16*)x;
   auto* G = (const __nv_bfloat16*)gamma;
   auto* RS = (const __nv_bfloat16*)resid;
   auto* DX = (__nv_bfloat16*)dx;
+  float* pgamma = scratch;
+  float* pbeta = scratch + (int64_t)ln_bwd_blocks() * d;
+  float* pdx = dx_col_sum != nullptr ? scratch + 2 * (int64_t)ln_bwd_blocks() * d : nullptr;
   switch (d / 128) {
-    case 8: ln_bwd_kernel<8, 4><<<blocks, 512, 0, s>>>(DY, X, mean, rstd, G, RS, DX, pgamma, pbeta, T, d); break;
-    case 16: ln_bwd_kernel<16, 4><<<blocks, 512, 0, s>>>(DY, X, mean, rstd, G, RS, DX, pgamma, pbeta, T, d); break;
-    case 32: ln_bwd_kernel<32, 2><<<blocks, 256, 0, s>>>(DY, X, mean, rstd, G, RS, DX, pgamma, pbeta, T, d); break;
+    case 8: ln_bwd_kernel<8, 4><<<blocks, 256, 0, s>>>(DY, X, mean, rstd, G, RS, DX, pgamma, pbeta, pdx, T, d); break;
+    case 16: ln_bwd_kernel<16, 4><<<blocks, 256, 0, s>>>(DY, X, mean, rstd, G, RS, DX, pgamma, pbeta, pdx, T, d); break;
+    case 32: ln_bwd_kernel<32, 1><<<blocks, 256, 0, s>>>(DY, X, mean, rstd, G, RS, DX, pgamma, pbeta, pdx, T, d); break;
     default: return cudaErrorInvalidValue;
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  ln_bwd_finalize_kernel<<<(d + 31) / 32, 256, 0, s>>>(pgamma, pbeta, blocks, d, (__nv_bfloat16*)dgamma,
-                                                         (__nv_bfloat16*)dbeta);
+  LnBwdFinalizeArgs f;
+  f.part[0] = pgamma, f.part[1] = pbeta, f.part[2] = pdx;
+  f.out[0] = (__nv_bfloat16*)dgamma, f.out[1] = (__nv_bfloat16*)dbeta, f.out[2] = (__nv_bfloat16*)dx_col_sum;
+  ln_bwd_finalize_kernel<<<dim3((d + 31) / 32, pdx != nullptr ? 3 : 2), 256, 0, s>>>(f, blocks, d);
   return cudaGetLastError();
 }
 

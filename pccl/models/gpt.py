@@ -183,19 +183,25 @@ def _fast(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.is_contiguous() and bool(_kernels())
 
 
-def _ln_bwd(dy, x, mean, rstd, w, b, gw, gb, resid=None):
-    """dx of a layer norm (+ ``resid``, the gradient flowing around it); writes gw, gb."""
+def _ln_bwd(dy, x, mean, rstd, w, b, gw, gb, resid=None, dx_sum=None):
+    """dx of a layer norm (+ ``resid``, the gradient flowing around it); writes gw, gb and, into
+    ``dx_sum`` when given, the column sums of dx (the bias gradient of the linear layer that
+    produced the normalised tensor's input)."""
     if _fast(dy) and _fast(x) and x.shape[-1] in (1024, 2048, 4096) and gw.is_contiguous() and gb.is_contiguous() \
-            and (resid is None or _fast(resid)):
+            and (resid is None or _fast(resid)) and (dx_sum is None or dx_sum.is_contiguous()):
         # one pass over dy and x: dx plus the weight/bias gradients, written in place
         global native_launches
         native_launches += 2
-        return _kernels().ln_bwd(dy, x, mean.view(-1), rstd.view(-1), w, gw, gb, resid)
+        return _kernels().ln_bwd(dy, x, mean.view(-1), rstd.view(-1), w, gw, gb, resid, dx_sum)
     dx, dw, db = torch.ops.aten.native_layer_norm_backward(dy, x, [x.shape[-1]], mean.view(-1, 1), rstd.view(-1, 1), w, b,
                                                            [True, True, True])
     gw.copy_(dw)
     gb.copy_(db)
-    return dx if resid is None else dx.add_(resid)
+    if resid is not None:
+        dx = dx.add_(resid)
+    if dx_sum is not None:
+        torch.sum(dx, dim=0, out=dx_sum)
+    return dx
 
 
 def _wgrad(dy: torch.Tensor, x: torch.Tensor, gw: torch.Tensor, gb: Optional[torch.Tensor]) -> None:
@@ -268,30 +274,52 @@ def layer_forward(x: torch.Tensor, p: Dict[str, torch.Tensor], cfg: GPTConfig, b
     return m.add_(x2), ctx
 
 
+def _cat_qkv_grads(dq, dk, dv, T: int, d: int, gb: torch.Tensor) -> torch.Tensor:
+    """[T, 3d] gradient of the packed QKV projection and its column sums (the QKV bias gradient).
+    The attention backward returns its gradients in the memory order of q, k, v ([B, S, H, dh]
+    underneath), so their [T, d] forms are views."""
+    parts = [t.transpose(1, 2).reshape(T, d) for t in (dq, dk, dv)]
+    if all(_fast(t) for t in parts) and d % 8 == 0 and gb.is_contiguous():
+        global native_launches
+        native_launches += 1
+        return _kernels().cat3_col_sum(parts[0], parts[1], parts[2], gb)
+    dqkv = torch.cat(parts, dim=1)
+    torch.sum(dqkv, dim=0, out=gb)
+    return dqkv
+
+
 def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[str, torch.Tensor], cfg: GPTConfig,
-                   batch: int) -> torch.Tensor:
-    """Returns dx; writes every parameter gradient of the layer into the views ``gr``."""
+                   batch: int, dy_sum: Optional[torch.Tensor] = None,
+                   dx_sum: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Returns dx; writes every parameter gradient of the layer into the views ``gr``.
+
+    ``dy_sum``: the column sums of ``dy`` when the kernel that produced ``dy`` already formed them
+    (they are this block's FC2 bias gradient).  ``dx_sum``: a [d] tensor that receives the column
+    sums of the returned dx, for the block below."""
     x, mean1, rstd1, h1, qd, kd, vd, att, a, x2, mean2, rstd2, h2, u, g = ctx
     T, d = x.shape
     S, H, dh = T // batch, cfg.n_head, cfg.head_dim
-    _wgrad(dy, g, gr["fc2_w"], gr["fc2_b"])
+    if dy_sum is not None:
+        gr["fc2_b"].copy_(dy_sum)
+        _wgrad(dy, g, gr["fc2_w"], None)
+    else:
+        _wgrad(dy, g, gr["fc2_w"], gr["fc2_b"])
     dg = torch.mm(dy, p["fc2_w"])
     du = _gelu_bwd(dg, u, gr["fc1_b"])
     del dg
     _wgrad(du, h2, gr["fc1_w"], None)
     dh2 = torch.mm(du, p["fc1_w"])
     del du
-    dx2 = _ln_bwd(dh2, x2, mean2, rstd2, p["ln2_w"], p["ln2_b"], gr["ln2_w"], gr["ln2_b"], resid=dy)
-    _wgrad(dx2, a, gr["proj_w"], gr["proj_b"])
+    # dx2 is the gradient of the attention projection's output: its column sums are proj_b's gradient
+    dx2 = _ln_bwd(dh2, x2, mean2, rstd2, p["ln2_w"], p["ln2_b"], gr["ln2_w"], gr["ln2_b"], resid=dy, dx_sum=gr["proj_b"])
+    _wgrad(dx2, a, gr["proj_w"], None)
     da = torch.mm(dx2, p["proj_w"])
     datt = da.view(batch, S, H, dh).transpose(1, 2)
     dq, dk, dv = torch.autograd.grad(att, (qd, kd, vd), datt)
-    # the attention backward returns its gradients in the memory order of q, k, v ([B, S, H, dh]
-    # underneath), so the [T, d] forms are views and one concatenation packs them as [T, 3d]
-    dqkv = torch.cat([t.transpose(1, 2).reshape(T, d) for t in (dq, dk, dv)], dim=1)
-    _wgrad(dqkv, h1, gr["qkv_w"], gr["qkv_b"])
+    dqkv = _cat_qkv_grads(dq, dk, dv, T, d, gr["qkv_b"])
+    _wgrad(dqkv, h1, gr["qkv_w"], None)
     dh1 = torch.mm(dqkv, p["qkv_w"])
-    dx = _ln_bwd(dh1, x, mean1, rstd1, p["ln1_w"], p["ln1_b"], gr["ln1_w"], gr["ln1_b"], resid=dx2)
+    dx = _ln_bwd(dh1, x, mean1, rstd1, p["ln1_w"], p["ln1_b"], gr["ln1_w"], gr["ln1_b"], resid=dx2, dx_sum=dx_sum)
     return dx
 
 
@@ -315,11 +343,12 @@ def embed_backward(dx: torch.Tensor, tokens: torch.Tensor, gr: Dict[str, torch.T
 def head_forward_backward(x: torch.Tensor, targets: torch.Tensor, p: Dict[str, torch.Tensor],
                           gr: Dict[str, torch.Tensor], cfg: GPTConfig, grad_scale: float, loss_sum: torch.Tensor,
                           ce_fwd_bwd: Callable, chunk_tokens: int = 4096,
-                          branch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          branch: Optional[torch.Tensor] = None, dx_sum: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Final layer norm, tied output projection and cross-entropy, forward and backward in
     one sweep over token chunks so the [T, vocab] logits never exist in full.  Adds the
     summed token losses to ``loss_sum``; writes gr["wte"], gr["lnf_*"]; returns dx.  With
-    ``branch`` the input is ``x + branch`` (see ``layer_forward_deferred``)."""
+    ``branch`` the input is ``x + branch`` (see ``layer_forward_deferred``); ``dx_sum`` receives the
+    column sums of the returned dx (see ``layer_backward``)."""
     T, d = x.shape
     hf, mean, rstd, x = _ln_fwd(x, p["lnf_w"], p["lnf_b"], cfg.ln_eps, branch)
     wte = p["wte"]
@@ -338,4 +367,4 @@ def head_forward_backward(x: torch.Tensor, targets: torch.Tensor, p: Dict[str, t
         else:
             gw.addmm_(logits.t(), hf[s:e])
         del logits
-    return _ln_bwd(dhf, x, mean, rstd, p["lnf_w"], p["lnf_b"], gr["lnf_w"], gr["lnf_b"])
+    return _ln_bwd(dhf, x, mean, rstd, p["lnf_w"], p["lnf_b"], gr["lnf_w"], gr["lnf_b"], dx_sum=dx_sum)

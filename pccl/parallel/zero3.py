@@ -183,6 +183,7 @@ class Zero3Engine:
         self.main = torch.cuda.current_stream(self.device)
         self._cur = None
         self._gemm_errs: List[torch.Tensor] = []
+        self._dx_sums = None
         self._fused_gid = None
         if self.fused_ag_gemm:
             from ..patch_deepspeed import get_heir_pg
@@ -302,8 +303,12 @@ class Zero3Engine:
         head_slot = (L + 1) % 2
         _wait(nxt)
         nxt = self._gather(L, 1 - head_slot) if L > 0 else None
+        # every kernel that produces a block's output gradient also sums its columns: that is the
+        # FC2 bias gradient of the block, handed down through two small buffers
+        if self._dx_sums is None:
+            self._dx_sums = [torch.empty(cfg.d_model, dtype=torch.bfloat16, device=self.device) for _ in range(2)]
         dx = gpt.head_forward_backward(x, targets, self.pviews[0][head_slot], self.gviews0, cfg, grad_scale,
-                                       self.loss_sum, self._ce, branch=branch)
+                                       self.loss_sum, self._ce, branch=branch, dx_sum=self._dx_sums[L % 2] if L > 0 else None)
         del branch
         # ---- backward through the blocks
         for li in range(L, 0, -1):
@@ -312,7 +317,8 @@ class Zero3Engine:
             nxt = self._gather(li - 1, 1 - slot) if li > 1 else None
             gslot = li % 2
             _wait(self._rs_pending[gslot])          # the buffer's previous reduce-scatter has read it
-            dx = gpt.layer_backward(dx, saved.pop(), self.pviews[li][slot], self.gviews[li][gslot], cfg, B)
+            dx = gpt.layer_backward(dx, saved.pop(), self.pviews[li][slot], self.gviews[li][gslot], cfg, B,
+                                    dy_sum=self._dx_sums[li % 2], dx_sum=self._dx_sums[(li - 1) % 2] if li > 1 else None)
             self._rs_pending[gslot] = self._reduce(li, None if self.local_only else self.gradbuf[gslot])
         gpt.embed_backward(dx, tokens, self.gviews0)
         rs0 = self._reduce(0, self.gradbuf0)

@@ -220,10 +220,32 @@ def test_layer_norm_backward_matches_fp32_reference(shape):
     torch.testing.assert_close(db.float(), br.grad, rtol=2e-2, atol=2e-2 * float(br.grad.abs().max()))
     # with the gradient that flows around the norm added in the same pass
     resid = torch.randn(T, d, device=DEV, generator=g).to(torch.bfloat16)
-    dx2 = pccl._C.ln_bwd(dy, x, mean.view(-1), rstd.view(-1), gamma, dg, db, resid)
+    dxs = torch.empty(d, device=DEV, dtype=torch.bfloat16)
+    dx2 = pccl._C.ln_bwd(dy, x, mean.view(-1), rstd.view(-1), gamma, dg, db, resid, dxs)
     want = xr.grad + resid.float()
     assert float((dx2.float() - want).norm() / want.norm()) < 1e-2
     torch.testing.assert_close(dg.float(), gr.grad, rtol=2e-2, atol=2e-2 * float(gr.grad.abs().max()))
+    torch.testing.assert_close(db.float(), br.grad, rtol=2e-2, atol=2e-2 * float(br.grad.abs().max()))
+    # ... and the column sums of dx
+    sums = dx2.float().sum(0)
+    torch.testing.assert_close(dxs.float(), sums, rtol=1e-2, atol=1e-2 * float(sums.abs().max()) + 1e-3)
+
+
+@pytest.mark.parametrize("shape", [(8192, 2048), (1000, 1024), (37, 8), (5, 24)])
+def test_concatenate_three_with_column_sums(shape):
+    import pccl
+
+    T, w = shape
+    g = torch.Generator(device=DEV).manual_seed(T + 5 * w)
+    parts = [torch.randn(T, w, device=DEV, generator=g).to(torch.bfloat16) for _ in range(3)]
+    gb = torch.empty(3 * w, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        gb.zero_()
+        cat = pccl._C.cat3_col_sum(parts[0], parts[1], parts[2], gb)
+        ref = torch.cat(parts, dim=1)
+        assert torch.equal(cat, ref)
+        sums = ref.float().sum(0)
+        torch.testing.assert_close(gb.float(), sums, rtol=1e-2, atol=1e-2 * float(sums.abs().max()) + 1e-3)
 
 
 @pytest.mark.parametrize("with_branch", [False, True])
@@ -297,8 +319,8 @@ def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm):
     before = gpt.native_launches
     loss = engine.train_step(tokens, targets)
     engine.check_errors()
-    # per block: 2 ln_fwd, gelu or gemm_gelu, gelu_bwd, 3 col_sum, 2 x (ln_bwd + finalize); head: ln_fwd, ln_bwd + finalize
-    assert gpt.native_launches - before == cfg.n_layer * 11 + 3
+    # per block: 2 ln_fwd, gelu or gemm_gelu, gelu_bwd, cat3, 2 x (ln_bwd + finalize); head: ln_fwd, ln_bwd + finalize
+    assert gpt.native_launches - before == cfg.n_layer * 9 + 3
     torch.testing.assert_close(loss[0], ref_loss, rtol=2e-2, atol=2e-2)
     for ui, u in enumerate(engine.units):
         got = gpt.views(u, engine.grad_shard[engine.shard_off[ui]:engine.shard_off[ui + 1]])

@@ -92,3 +92,73 @@ def test_group_type_is_checked():
         pccl._reduce_scatter(torch.empty(2), torch.empty(4), group=42)
     with pytest.raises(TypeError):
         pccl._all_reduce(torch.empty(2), group=3.5)
+
+
+def test_layer_math_fallback_matches_autograd_on_cpu():
+    """The hand-written forward/backward of the GPT blocks (pure-PyTorch paths: residual adds
+    deferred to the layer norms, bias gradients handed down as column sums) against autograd."""
+    import torch.nn.functional as F
+
+    from pccl.models import gpt
+
+    torch.manual_seed(0)
+    cfg = GPTConfig(2, 64, 4, 256, vocab=96, seq_len=16, name="cpu-test")
+    units = unit_specs(cfg)
+    B, S = 2, cfg.seq_len
+    T = B * S
+    flats = [torch.zeros(u.numel, dtype=torch.float64) for u in units]
+    for u, f in zip(units, flats):
+        gpt.init_unit(u, f, cfg, seed=7)
+        f.add_(torch.randn_like(f) * 0.02)                       # biases and norms away from 0 / 1
+    params = [gpt.views(u, f) for u, f in zip(units, flats)]
+    grads = [gpt.views(u, torch.zeros_like(f)) for u, f in zip(units, flats)]
+    tokens = torch.randint(0, cfg.vocab, (B, S))
+    targets = torch.randint(0, cfg.vocab, (B, S))
+
+    def ce(logits, tgt, loss_sum, grad_scale):
+        lp = torch.log_softmax(logits, dim=-1)
+        loss_sum += -lp.gather(1, tgt.view(-1, 1)).sum()
+        g = lp.exp()
+        g.scatter_add_(1, tgt.view(-1, 1), -torch.ones(len(tgt), 1, dtype=g.dtype))
+        logits.copy_(g * grad_scale)
+
+    with torch.no_grad():
+        x = gpt.embed_forward(tokens, params[0])
+        branch, saved = None, []
+        for li in range(1, cfg.n_layer + 1):
+            x, branch, ctx = gpt.layer_forward_deferred(x, branch, params[li], cfg, B)
+            saved.append(ctx)
+        loss_sum = torch.zeros(1, dtype=torch.float64)
+        sums = [torch.empty(cfg.d_model, dtype=torch.float64) for _ in range(2)]
+        L = cfg.n_layer
+        dx = gpt.head_forward_backward(x, targets, params[0], grads[0], cfg, 1.0 / T, loss_sum, ce, chunk_tokens=20,
+                                       branch=branch, dx_sum=sums[L % 2])
+        for li in range(L, 0, -1):
+            dx = gpt.layer_backward(dx, saved.pop(), params[li], grads[li], cfg, B, dy_sum=sums[li % 2],
+                                    dx_sum=sums[(li - 1) % 2] if li > 1 else None)
+        gpt.embed_backward(dx, tokens, grads[0])
+
+    ref = [{k: v.clone().requires_grad_() for k, v in p.items()} for p in params]
+    p0 = ref[0]
+    h = F.embedding(tokens, p0["wte"]) + p0["wpe"][:S]
+    for p in ref[1:]:
+        n = F.layer_norm(h, (cfg.d_model,), p["ln1_w"], p["ln1_b"], cfg.ln_eps)
+        qkv = F.linear(n, p["qkv_w"], p["qkv_b"]).view(B, S, 3, cfg.n_head, cfg.head_dim)
+        q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, cfg.d_model)
+        h = h + F.linear(a, p["proj_w"], p["proj_b"])
+        n = F.layer_norm(h, (cfg.d_model,), p["ln2_w"], p["ln2_b"], cfg.ln_eps)
+        h = h + F.linear(F.gelu(F.linear(n, p["fc1_w"], p["fc1_b"]), approximate="tanh"), p["fc2_w"], p["fc2_b"])
+    h = F.layer_norm(h, (cfg.d_model,), p0["lnf_w"], p0["lnf_b"], cfg.ln_eps)
+    loss = F.cross_entropy(F.linear(h, p0["wte"]).view(T, -1), targets.reshape(-1))
+    loss.backward()
+    torch.testing.assert_close(loss_sum[0] / T, loss.detach(), rtol=1e-9, atol=1e-9)
+    for ui in range(len(units)):
+        for name, r in ref[ui].items():
+            torch.testing.assert_close(grads[ui][name], r.grad, rtol=1e-7, atol=1e-9, msg=lambda m: f"unit {ui} {name}: {m}")
+    # the one-call form sums the residual itself
+    with torch.no_grad():
+        x0 = gpt.embed_forward(tokens, params[0])
+        y, _ctx = gpt.layer_forward(x0, params[1], cfg, B)
+        x2, m, _ctx = gpt.layer_forward_deferred(x0, None, params[1], cfg, B)
+    torch.testing.assert_close(y, x2 + m)
