@@ -43,7 +43,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded: gives up after the communicator's time budget.
+// Bounded: gives up after the communicator's time limit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t timeout_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
@@ -100,7 +100,7 @@ __device__ __forceinline__ bool bulk_ok(const void* a, const void* b, uint64_t b
 
 // Copy `bytes` from src to each of dsts[0..ndst).  Called by all threads; thread 0 drives the
 // copy engine.  On return the stores are ISSUED, not complete: call cta_bulk_flush() before
-// publishing a flag.  Returns false if a load did not arrive within the time budget.
+// publishing a flag.  Returns false if a load did not arrive within the time limit.
 __device__ __forceinline__ bool cta_bulk_copy(BulkPipe& p, char* const* dsts, int ndst, const char* src, uint64_t bytes) {
   const uint32_t nchunks = (uint32_t)((bytes + kBulkStageBytes - 1) / kBulkStageBytes);
   __shared__ int s_bulk_ok;

@@ -70,7 +70,7 @@ struct GroupDev {
   char* mc_heap;                     // multicast alias of the heaps (NVLS) or nullptr
   Status* status[kMaxRanks];         // per local rank (index by blockIdx.y); device-visible pinned memory
   uint32_t* poison[kMaxRanks];       // per local rank device word: non-zero once any lane failed
-  uint64_t timeout_ns;               // budget of every single wait
+  uint64_t timeout_ns;               // time limit of every single wait
 };
 
 enum DType : int { kBF16 = 0, kF16 = 1, kF32 = 2 };

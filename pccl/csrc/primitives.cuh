@@ -70,7 +70,7 @@ __device__ __forceinline__ void report_failure(const GroupDev& g, int li, uint32
   if (g.poison[li] != nullptr) atomicExch(g.poison[li], 1u);
 }
 
-// One thread spins until flag >= epoch (wrap-safe), the budget runs out, or the
+// One thread spins until flag >= epoch (wrap-safe), the time limit runs out, or the
 // communicator is poisoned.  Never traps, never spins without a limit.
 __device__ __forceinline__ bool spin_until(const uint32_t* flag, uint32_t epoch, const GroupDev& g, int li,
                                            uint32_t* seen_out) {

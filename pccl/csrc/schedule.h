@@ -107,7 +107,7 @@ PCCL_HD Step rs_step(int algo, int P, int r, int t) {
     s.nblocks = 1;
   } else if (algo == kRecursive) {
     const int G = P >> t;       // size of the group still exchanging
-    const int h = G >> 1;       // blocks exchanged this round
+    const int h = G >> 1;       // blocks exchanged this step
     const int base = (r / G) * G;  // first block of the active region of this rank
     if (r - base < h) {         // lower half keeps [base, base+h), sends [base+h, base+G)
       s.dst = s.src = r + h;

@@ -508,7 +508,7 @@ cudaError_t launch_ln_bwd(const void* dy, const void* x, const float* mean, cons
                           const void* resid, void* dgamma, void* dbeta, void* dx_col_sum, float* scratch, int64_t T, int d,
                           cudaStream_t s) {
   if (T <= 0) return cudaSuccess;
-  const int rb = d <= 2048 ? 4 : 1;          // rows per group per iteration (register budget)
+  const int rb = d <= 2048 ? 4 : 1;          // rows per group per iteration (limited by registers)
   int blocks = ln_bwd_blocks();
   if ((int64_t)blocks * 2 * rb > T) blocks = (int)((T + 2 * rb - 1) / (2 * rb));
   auto* DY = (const __nv_bfloat16*)dy;

@@ -2,7 +2,7 @@
 
 The reference ends the process on any CUDA error (``CUDA_CHECK`` prints and calls
 ``exit(1)``, ``pccl/include/common.h:8-15``) and hangs forever when a peer is missing.
-Here every device-side wait has a budget, and an expired one becomes an exception.
+Here every device-side wait has a time limit, and an expired one becomes an exception.
 """
 
 

@@ -257,7 +257,7 @@ def test_argument_checks():
 
 
 def test_bounded_wait_reports_timeout_and_context_survives():
-    """A rank whose peers never show up: the kernel gives up after its budget, says where,
+    """A rank whose peers never show up: the kernel gives up after its time limit, says where,
     and returns.  Nothing traps; the device stays usable; recover() clears the failure."""
     comm = pccl.Communicator.with_fake_peers(2, rank=0, device=0, timeout_ms=50.0)
     x = torch.ones(1000, device=DEV)
