@@ -1,6 +1,7 @@
 """Shared plumbing of the collective entry points: algorithm naming, async launch."""
 from __future__ import annotations
 
+import os
 from typing import Callable, Optional
 
 import torch
@@ -20,10 +21,26 @@ def algo_from_flags(algorithm: Optional[str], recursive_flag: bool) -> str:
     return sch.RECURSIVE if recursive_flag else sch.RING
 
 
-def run_native(group: Group, async_op: bool, launch: Callable[[], None]) -> Optional[Request]:
+# NVTX range around every native collective launch (name, algorithm, bytes, group size, lanes), for
+# timeline tools; off unless PCCL_NVTX=1 or this flag is set.  The reference's only ranges are the
+# record_function wrappers of its benchmark loop (benchmark_raw_collectives/utils.py:20,27).
+NVTX = os.environ.get("PCCL_NVTX", "0") == "1"
+
+
+def run_native(group: Group, async_op: bool, launch: Callable[[], None],
+               label: Optional[Callable[[], str]] = None) -> Optional[Request]:
     """Enqueue ``launch()`` on the current stream, or, for ``async_op``, on the
     communicator's side stream after everything the current stream has queued so far."""
     comm = group.comm
+    if NVTX and label is not None:
+        inner, name = launch, label()
+
+        def launch():
+            torch.cuda.nvtx.range_push(name)
+            try:
+                inner()
+            finally:
+                torch.cuda.nvtx.range_pop()
     if not async_op:
         launch()
         return None

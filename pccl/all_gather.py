@@ -75,7 +75,8 @@ def _all_gather(output_tensor: torch.Tensor, input_tensor: torch.Tensor,
         def launch():
             native.all_gather(group.gid, [output_tensor], [input_tensor], sch.ALGO_IDS[algo], nl)
 
-        return run_native(group, async_op, launch)
+        return run_native(group, async_op, launch,
+                          lambda: f"pccl.all_gather {algo} {nbytes}B/rank P={group.size} lanes={nl}")
     if algo == sch.AUTO:
         algo = sch.RECURSIVE if sch.is_pow2(group.size) else sch.RING
     p2p.all_gather(output_tensor, input_tensor, group.transport(), algo)

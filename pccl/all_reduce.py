@@ -50,7 +50,8 @@ def _all_reduce(input_tensor: torch.Tensor, group: Optional[Union[dist.ProcessGr
         def launch():
             native.all_reduce(group.gid, [input_tensor], algo_id, nl, scale)
 
-        return run_native(group, async_op, launch)
+        return run_native(group, async_op, launch,
+                          lambda: f"pccl.all_reduce {algo} {nbytes}B P={group.size} lanes={nl}")
     algo = algorithm if algorithm in (sch.RING, sch.RECURSIVE, sch.DIRECT) else None
     if algo is None:
         algo = sch.RECURSIVE if (use_rh_and_rd and sch.is_pow2(group.size)) else sch.RING
@@ -82,7 +83,7 @@ def broadcast(tensor: torch.Tensor, src: int, group=None, async_op: bool = False
         def launch():
             native.broadcast(group.gid, [tensor], src, nl, comm.nvls)
 
-        return run_native(group, async_op, launch)
+        return run_native(group, async_op, launch, lambda: f"pccl.broadcast root={src} {nbytes}B P={group.size} lanes={nl}")
     p2p.broadcast(tensor, src, group.transport())
     return completed_request() if async_op else None
 
@@ -97,7 +98,7 @@ def barrier(group=None, async_op: bool = False, host_sync: bool = True) -> Optio
     if group.native:
         comm = group.comm
         native = comm.native
-        req = run_native(group, async_op, lambda: native.barrier(group.gid))
+        req = run_native(group, async_op, lambda: native.barrier(group.gid), lambda: f"pccl.barrier P={group.size}")
         if host_sync and not async_op:
             comm.check(sync=True)
         return req

@@ -173,6 +173,10 @@ class Communicator:
         if timeout_ms is None:
             timeout_ms = float(os.environ.get("PCCL_TIMEOUT_MS", "20000"))
         self.native.set_timeout_ms(timeout_ms)
+        jitter_us = float(os.environ.get("PCCL_DEBUG_JITTER_US", "0"))
+        trace_events = int(os.environ.get("PCCL_TRACE_EVENTS", "0"))
+        if jitter_us > 0 or trace_events > 0:
+            self.native.set_debug(int(jitter_us * 1000), trace_events)
         self.world_group = self._register_group(list(range(self.world)), p2p_timeout)
         dist.barrier(group=pg)   # every peer has mapped everything before the first kernel
         atexit.register(_close_weak, weakref.ref(self))
@@ -442,6 +446,36 @@ class Communicator:
                 if st["code"] == 1:
                     raise PcclTimeoutError(msg)
                 raise PcclPoisonedError(msg)
+
+    # ------------------------------------------------------------------ debugging aids
+    def set_debug(self, jitter_us: float = 0.0, trace_events: int = 0) -> None:
+        """Stress mode and device-side trace, both off by default.
+
+        ``jitter_us`` > 0: every lane of every kernel of this communicator sleeps a pseudo-random
+        time below that before each wait and each signal, so ranks and lanes meet in orders a quiet
+        machine never produces; results must not change (the GPU tests run the collectives this
+        way against their references).  ``trace_events`` > 0: the kernels record every completed
+        wait and published flag (time, call number, rank, lane, flag kind) in device memory;
+        ``trace()`` reads them.  Also set from ``PCCL_DEBUG_JITTER_US`` / ``PCCL_TRACE_EVENTS``
+        when the communicator is created.  The reference has neither: its only hook is
+        ``record_function`` around benchmark iterations (``benchmark_raw_collectives/utils.py:20,27``)."""
+        if self.native is None:
+            return
+        torch.cuda.synchronize(self.device)
+        self.native.set_debug(int(jitter_us * 1000), int(trace_events))
+
+    def trace(self):
+        """Device-side trace since the last call: ``(events, dropped)`` with one dict per event,
+        sorted by time.  Synchronises the device."""
+        if self.native is None:
+            return [], 0
+        rows, dropped = self.native.read_trace()
+        events = [{"t_ns": t, "call": epoch, "rank": rank, "lane": lane,
+                   "flag": _KIND_NAMES.get(kind, f"step{kind - 2}"), "op": "signal" if sig else "wait",
+                   "collective": _COLL_NAMES.get(coll, coll)}
+                  for (t, epoch, rank, lane, kind, sig, coll) in rows]
+        events.sort(key=lambda e: e["t_ns"])
+        return events, int(dropped)
 
     def recover(self) -> None:
         """Forget a failure.  Every surviving rank must call it at the same point; the host

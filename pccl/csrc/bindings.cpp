@@ -508,6 +508,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("group_size", &Comm::group_size)
       .def("group_rank", &Comm::group_rank)
       .def("set_timeout_ms", &Comm::set_timeout_ms)
+      .def("set_debug", &Comm::set_debug, py::arg("jitter_ns") = 0, py::arg("trace_events") = 0,
+           "stress-mode jitter before every wait/signal and capacity of the device-side trace (0 = off)")
+      .def("read_trace",
+           [](Comm& c) {
+             uint64_t dropped = 0;
+             std::vector<TraceEvent> ev = c.read_trace(&dropped);
+             py::list rows;
+             for (const TraceEvent& e : ev)
+               rows.append(py::make_tuple(e.t_ns, e.epoch, (int)e.rank, (int)e.lane, (int)(e.what & 63), (e.what & 64) != 0,
+                                          e.collective));
+             return py::make_tuple(rows, dropped);
+           },
+           "([(t_ns, epoch, rank, lane, slot_kind, is_signal, collective)], dropped); empties the trace")
       .def("timeout_ms", &Comm::timeout_ms)
       .def("status", &status_dict, py::arg("local_slot") = 0)
       .def("poisoned", &Comm::poisoned)

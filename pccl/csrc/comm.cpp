@@ -97,6 +97,42 @@ Comm::~Comm() {
     if (g.tail) cudaEventDestroy(g.tail);
   if (status_) cudaFreeHost(status_);
   if (poison_) cudaFree(poison_);
+  if (trace_) cudaFree(trace_);
+}
+
+void Comm::set_debug(uint64_t jitter_ns, uint64_t trace_events) {
+  if (jitter_ns > 10ull * 1000 * 1000) throw Error("jitter above 10 ms per synchronisation point is refused");
+  if (trace_events > (1ull << 24)) throw Error("trace capacity above 16 Mi records is refused");
+  jitter_ns_ = (uint32_t)jitter_ns;
+  if (trace_ != nullptr && trace_events != trace_capacity_) {
+    PCCL_CUDA(cudaDeviceSynchronize());
+    PCCL_CUDA(cudaFree(trace_));
+    trace_ = nullptr;
+    trace_capacity_ = 0;
+  }
+  if (trace_events > 0 && trace_ == nullptr) {
+    const size_t bytes = sizeof(TraceBuf) + (size_t)trace_events * sizeof(TraceEvent);
+    PCCL_CUDA(cudaMalloc(reinterpret_cast<void**>(&trace_), bytes));
+    PCCL_CUDA(cudaMemset(trace_, 0, bytes));
+    const uint32_t cap = (uint32_t)trace_events;
+    PCCL_CUDA(cudaMemcpy(&trace_->capacity, &cap, sizeof(cap), cudaMemcpyHostToDevice));
+    trace_capacity_ = cap;
+  }
+}
+
+std::vector<TraceEvent> Comm::read_trace(uint64_t* dropped) {
+  std::vector<TraceEvent> out;
+  if (dropped) *dropped = 0;
+  if (trace_ == nullptr) return out;
+  PCCL_CUDA(cudaDeviceSynchronize());
+  unsigned long long count = 0;
+  PCCL_CUDA(cudaMemcpy(&count, &trace_->count, sizeof(count), cudaMemcpyDeviceToHost));
+  const uint64_t kept = count < trace_capacity_ ? count : trace_capacity_;
+  out.resize(kept);
+  if (kept > 0) PCCL_CUDA(cudaMemcpy(out.data(), trace_->ev, kept * sizeof(TraceEvent), cudaMemcpyDeviceToHost));
+  if (dropped) *dropped = count - kept;
+  PCCL_CUDA(cudaMemset(&trace_->count, 0, sizeof(count)));
+  return out;
 }
 
 int64_t Comm::alloc(uint64_t bytes, uint64_t align) {
@@ -186,6 +222,8 @@ void Comm::begin_call(int gid, GroupDev* g, cudaStream_t stream) {
   g->size = P;
   g->epoch = gs.epoch;
   g->timeout_ns = timeout_ns_;
+  g->trace = trace_;
+  g->jitter_ns = jitter_ns_;
   g->mc_heap = (char*)mc_heap_;
   for (int i = 0; i < P; ++i) {
     g->heap[i] = (char*)heaps_[gs.ranks[i]];

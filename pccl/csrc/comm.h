@@ -112,6 +112,15 @@ class Comm {
   void broadcast(int gid, BroadcastArgs a, int nlanes, cudaStream_t stream);
   void barrier(int gid, cudaStream_t stream);
 
+  // ---- debugging aids, both off by default
+  // Stress mode: every lane sleeps a pseudo-random time below `jitter_ns` (at most 10 ms) before
+  // each wait and signal.  Trace: keep up to `trace_events` records of passed synchronisation
+  // points in device memory (0 frees the buffer).  Call with no kernel of the communicator in flight.
+  void set_debug(uint64_t jitter_ns, uint64_t trace_events);
+  // Synchronises the device, copies the trace out and empties it.  Also returns how many
+  // records did not fit.
+  std::vector<TraceEvent> read_trace(uint64_t* dropped);
+
   // Fill `g` for a launch on `stream` (also used by fused kernels living in other files).
   void begin_call(int gid, GroupDev* g, cudaStream_t stream);
   uint64_t kernels_launched() const { return launches_; }
@@ -130,6 +139,9 @@ class Comm {
   uint64_t timeout_ns_ = 20ull * 1000 * 1000 * 1000;
   int max_lanes_ = 0;
   uint64_t launches_ = 0;
+  TraceBuf* trace_ = nullptr;     // device
+  uint32_t trace_capacity_ = 0;
+  uint32_t jitter_ns_ = 0;
   mutable std::mutex mu_;
 };
 

@@ -59,6 +59,25 @@ enum CollectiveId : uint32_t {
   kCollWaitProbe = 7,
 };
 
+// ------------------------------------------------------------------ optional device-side trace
+// One record per synchronisation point a lane passed (a completed wait or a published flag), in
+// the order the records were claimed.  The buffer is plain device memory read back on request.
+struct TraceEvent {
+  uint64_t t_ns;       // %globaltimer
+  uint32_t epoch;      // call number within the group
+  uint16_t lane;
+  uint8_t rank;        // group index of the lane's rank
+  uint8_t what;        // bits 0-5: slot kind; bit 6: signal (else wait); bit 7: reserved
+  uint32_t collective; // CollectiveId
+  uint32_t pad;
+};
+struct TraceBuf {
+  unsigned long long count;   // records claimed so far (may exceed capacity: the rest was dropped)
+  uint32_t capacity;
+  uint32_t pad;
+  TraceEvent ev[1];           // capacity records follow
+};
+
 // ------------------------------------------------------------------ group as the kernel sees it
 struct GroupDev {
   int size;                          // P
@@ -71,6 +90,8 @@ struct GroupDev {
   Status* status[kMaxRanks];         // per local rank (index by blockIdx.y); device-visible pinned memory
   uint32_t* poison[kMaxRanks];       // per local rank device word: non-zero once any lane failed
   uint64_t timeout_ns;               // time limit of every single wait
+  TraceBuf* trace;                   // nullptr unless tracing is switched on
+  uint32_t jitter_ns;                // stress mode: every lane sleeps a pseudo-random time below this before each wait and signal
 };
 
 enum DType : int { kBF16 = 0, kF16 = 1, kF32 = 2 };

@@ -99,14 +99,52 @@ struct LaneCtx {
   uint32_t coll;
 };
 
+// Debug hooks of every synchronisation point; both are off (two predictable branches) unless the
+// communicator switched them on.  Called by one thread.
+//  * stress mode: sleep a pseudo-random, bounded time, so that lanes and ranks meet their waits
+//    and signals in orders a quiet machine never produces; results must not change.
+//  * trace: append (time, epoch, rank, lane, slot kind, wait|signal) to the trace buffer.
+__device__ __forceinline__ void debug_jitter(const GroupDev& g, const LaneCtx& c, int kind) {
+  if (g.jitter_ns == 0u) return;
+  uint32_t h = g.epoch * 0x9E3779B1u ^ (uint32_t)c.lane * 0x85EBCA77u ^ (uint32_t)c.me * 0xC2B2AE3Du ^ (uint32_t)kind * 0x27D4EB2Fu ^
+               (uint32_t)global_timer_ns();
+  h ^= h >> 15;
+  h *= 0x2C1B3C6Du;
+  h ^= h >> 12;
+  uint32_t ns = h % g.jitter_ns;
+  while (ns > 0u) {                       // at most jitter_ns in total
+    const uint32_t step = ns < 500000u ? ns : 500000u;
+    __nanosleep(step);
+    ns -= step;
+  }
+}
+__device__ __forceinline__ void debug_trace(const GroupDev& g, const LaneCtx& c, int kind, bool is_signal) {
+  TraceBuf* tb = g.trace;
+  if (tb == nullptr) return;
+  const unsigned long long i = atomicAdd(&tb->count, 1ull);
+  if (i < tb->capacity) {
+    TraceEvent e;
+    e.t_ns = global_timer_ns();
+    e.epoch = g.epoch;
+    e.lane = (uint16_t)c.lane;
+    e.rank = (uint8_t)c.me;
+    e.what = (uint8_t)((kind & 63) | (is_signal ? 64 : 0));
+    e.collective = c.coll;
+    e.pad = 0;
+    tb->ev[i] = e;
+  }
+}
+
 // All threads of the CTA call this; thread 0 waits.  Returns false (to all threads) when
 // the wait gave up; the status word then says where.
 __device__ __forceinline__ bool cta_wait(const GroupDev& g, const LaneCtx& c, int kind, int src) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
+    debug_jitter(g, c, kind);
     uint32_t seen = 0;
     const uint32_t* flag = g.sig[c.me] + slot_index(c.lane, kind, src);
     bool ok = spin_until(flag, g.epoch, g, c.li, &seen);
+    if (ok) debug_trace(g, c, kind, false);
     if (!ok) {
       const bool poisoned = g.poison[c.li] != nullptr &&
                             *reinterpret_cast<const volatile uint32_t*>(g.poison[c.li]) != 0u;
@@ -123,7 +161,10 @@ __device__ __forceinline__ bool cta_wait(const GroupDev& g, const LaneCtx& c, in
 // Wait for the same slot kind from every member whose bit is set in `mask`.
 __device__ __forceinline__ bool cta_wait_mask(const GroupDev& g, const LaneCtx& c, int kind, unsigned mask) {
   __shared__ int s_ok_all;
-  if (threadIdx.x == 0) s_ok_all = 1;
+  if (threadIdx.x == 0) {
+    s_ok_all = 1;
+    debug_jitter(g, c, kind);
+  }
   __syncthreads();
   if (threadIdx.x < (unsigned)g.size && ((mask >> threadIdx.x) & 1u)) {
     uint32_t seen = 0;
@@ -138,6 +179,7 @@ __device__ __forceinline__ bool cta_wait_mask(const GroupDev& g, const LaneCtx& 
   }
   __syncthreads();
   const int ok = s_ok_all;
+  if (ok != 0 && threadIdx.x == 0) debug_trace(g, c, kind, false);
   __syncthreads();
   return ok != 0;
 }
@@ -145,6 +187,10 @@ __device__ __forceinline__ bool cta_wait_mask(const GroupDev& g, const LaneCtx& 
 // Publish slot(lane, kind, me) = epoch in the pad of every member in `mask`.
 // The leading bar.sync orders every thread's earlier stores before the release.
 __device__ __forceinline__ void cta_signal_mask(const GroupDev& g, const LaneCtx& c, int kind, unsigned mask) {
+  if (threadIdx.x == 0) {
+    debug_jitter(g, c, kind);          // the whole CTA waits at the barrier below: the flags go out late
+    debug_trace(g, c, kind, true);
+  }
   __syncthreads();
   if (threadIdx.x < (unsigned)g.size && ((mask >> threadIdx.x) & 1u)) {
     __threadfence_system();

@@ -277,6 +277,50 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     comm.recover()
 
 
+@pytest.mark.parametrize("P", [4, 8])
+def test_stress_mode_keeps_results_and_trace_records_the_protocol(P):
+    """Every lane sleeps a pseudo-random time before each wait and signal, so ranks and lanes
+    meet in orders a quiet GPU never produces: results must stay bit-exact (all-gather) or equal
+    to the fp32 reference (reduce-scatter).  The device-side trace of the same calls shows every
+    rank signalling and waiting."""
+    comm = pccl.Communicator.emulated_world(P, device=0, heap_bytes=64 << 20, staging_bytes=16 << 20)
+    comm.set_debug(jitter_us=150.0, trace_events=1 << 16)
+    gid = comm.world_group.gid
+    n = 40000 + 3
+    for rep in range(3):                               # back-to-back calls reuse flags and staging
+        for algo in (sch.DIRECT, sch.RING, sch.RECURSIVE, sch.PULL):
+            ins = [rand(n, torch.bfloat16, 100 * rep + 7 * r) for r in range(P)]
+            outs = [torch.zeros(P * n, dtype=torch.bfloat16, device=DEV) for _ in range(P)]
+            comm.native.all_gather(gid, outs, ins, sch.ALGO_IDS[algo], 4)
+            want = torch.cat(ins)
+            comm.check()
+            for r in range(P):
+                assert torch.equal(outs[r], want), f"all_gather {algo} rep {rep} rank {r}"
+        for algo in (sch.DIRECT, sch.RING, sch.RECURSIVE):
+            ins = [rand(P * n, torch.bfloat16, 1000 * rep + 11 * r) for r in range(P)]
+            outs = [torch.zeros(n, dtype=torch.float32, device=DEV) for _ in range(P)]
+            comm.native.reduce_scatter(gid, outs, ins, sch.ALGO_IDS[algo], 4, 1.0 / P, None)
+            comm.check()
+            want = rs_reference(ins, P, n, 1.0 / P, torch.float32)
+            for r in range(P):
+                torch.testing.assert_close(outs[r], want[r], rtol=2e-2, atol=2e-2)
+    events, dropped = comm.trace()
+    assert dropped == 0 and len(events) > 0
+    assert {e["rank"] for e in events} == set(range(P))
+    assert {"signal", "wait"} <= {e["op"] for e in events}
+    assert {"all_gather", "reduce_scatter"} <= {e["collective"] for e in events}
+    assert all(a["t_ns"] <= b["t_ns"] for a, b in zip(events, events[1:]))
+    # per rank and lane, call numbers never go backwards
+    last = {}
+    for e in events:
+        key = (e["rank"], e["lane"])
+        assert e["call"] >= last.get(key, 0)
+        last[key] = e["call"]
+    assert comm.trace() == ([], 0)                      # reading empties it
+    comm.set_debug(0.0, 0)
+    comm.close()
+
+
 def test_python_api_on_single_rank_world():
     """world == 1: every collective degenerates to a local copy / scale through the kernels."""
     comm = pccl.Communicator.emulated_world(1, device=0, heap_bytes=4 << 20, staging_bytes=1 << 20)
