@@ -73,6 +73,17 @@ def test_linear_wrapper_and_identity():
     check_close(y.view(-1, 512), x.view(-1, K).float() @ w.float().t(), K)
     with pytest.raises(RuntimeError):
         linear(rnd((4, 12), 1), rnd((8, 12), 2))   # K not a multiple of 8
+    # one-CTA form through the wrapper, and the two-output form
+    y1 = linear(x, w, check=True, two_cta=False)
+    assert torch.equal(y1, y)
+    from pccl.ops.gemm import linear_gelu
+
+    b = rnd((512,), 7)
+    u, g = linear_gelu(x, w, b, check=True)
+    assert u.shape == (3, 50, 512) and g.shape == u.shape
+    check_close(u.view(-1, 512), x.view(-1, K).float() @ w.float().t() + b.float(), K)
+    ref_g = torch.nn.functional.gelu(u.float(), approximate="tanh")
+    assert float((g.float() - ref_g).abs().max()) <= 1e-2 * float(ref_g.abs().max()) + 1e-3
 
 
 @pytest.mark.parametrize("two_cta", [False, True], ids=["one_sm", "cta_pair"])
