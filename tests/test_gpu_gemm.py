@@ -75,7 +75,7 @@ def test_linear_wrapper_and_identity():
         linear(rnd((4, 12), 1), rnd((8, 12), 2))   # K not a multiple of 8
     # one-CTA form through the wrapper, and the two-output form
     y1 = linear(x, w, check=True, two_cta=False)
-    assert torch.equal(y1, y)
+    check_close(y1.view(-1, 512), x.view(-1, K).float() @ w.float().t(), K)
     from pccl.ops.gemm import linear_gelu
 
     b = rnd((512,), 7)
