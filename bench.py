@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--nvls", type=int, default=int(os.environ.get("PCCL_ENABLE_NVLS", "0")))
     ap.add_argument("--fused-ag-gemm", type=int, default=int(os.environ.get("PCCL_FUSED_AG_GEMM", "0")))
     ap.add_argument("--gather-ctas", type=int, default=16)
+    ap.add_argument("--overlap-wgrad", type=int, default=int(os.environ.get("PCCL_OVERLAP_WGRAD", "0")),
+                    help="weight-gradient GEMMs on a second stream beside the memory-bound backward kernels")
     ap.add_argument("--fused-gelu-gemm", type=int, default=int(os.environ.get("PCCL_FUSED_GELU_GEMM", "0")),
                     help="FC1 on the library's tcgen05 GEMM with bias+GELU in the epilogue")
     ap.add_argument("--no-e2e", action="store_true")
@@ -107,7 +109,7 @@ def main() -> None:
     backend = TorchBackend()
     engine = Zero3Engine(cfg, backend, OptimConfig(), device=dev, comm=comm, micro_batch=mb,
                          fused_ag_gemm=(args.impl == "pccl" and bool(args.fused_ag_gemm)), gather_ctas=args.gather_ctas,
-                         fused_gelu_gemm=bool(args.fused_gelu_gemm))
+                         fused_gelu_gemm=bool(args.fused_gelu_gemm), overlap_wgrad=bool(args.overlap_wgrad))
 
     total_steps = warmup + args.steps
     gen = torch.Generator(device="cpu").manual_seed(4321 + rank)
@@ -192,6 +194,7 @@ def main() -> None:
                 "parallelism": f"zero3-dp{world}", "optimizer": "AdamW fp32 master+moments, grad-norm clip 1.0",
                 "algorithm": args.algorithm, "lanes": args.lanes, "nvls": bool(args.nvls),
                 "fused_ag_gemm": bool(engine.fused_ag_gemm), "fused_gelu_gemm": bool(engine.fused_gelu_gemm),
+                "overlap_wgrad": bool(engine.overlap_wgrad),
                 "l2": "working set per step (tens of GB) exceeds the 126 MB L2; no explicit flush",
                 "transport": comm.transport_name if comm is not None else "nccl",
             },

@@ -204,15 +204,14 @@ def _ln_bwd(dy, x, mean, rstd, w, b, gw, gb, resid=None, dx_sum=None):
     return dx
 
 
-def _wgrad(dy: torch.Tensor, x: torch.Tensor, gw: torch.Tensor, gb: Optional[torch.Tensor]) -> None:
-    torch.mm(dy.t(), x, out=gw)
-    if gb is not None:
-        if _fast(dy) and dy.shape[1] % 8 == 0 and gb.is_contiguous():
-            global native_launches
-            native_launches += 1
-            _kernels().col_sum(dy, gb)
-        else:
-            torch.sum(dy, dim=0, out=gb)
+def _bias_grad(dy: torch.Tensor, gb: torch.Tensor) -> None:
+    """gb = column sums of dy."""
+    if _fast(dy) and dy.shape[1] % 8 == 0 and gb.is_contiguous():
+        global native_launches
+        native_launches += 1
+        _kernels().col_sum(dy, gb)
+    else:
+        torch.sum(dy, dim=0, out=gb)
 
 
 def _fc1_gelu(h: torch.Tensor, p: Dict[str, torch.Tensor], linear_fwd: LinearFwd):
@@ -289,37 +288,51 @@ def _cat_qkv_grads(dq, dk, dv, T: int, d: int, gb: torch.Tensor) -> torch.Tensor
 
 
 def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[str, torch.Tensor], cfg: GPTConfig,
-                   batch: int, dy_sum: Optional[torch.Tensor] = None,
-                   dx_sum: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   batch: int, dy_sum: Optional[torch.Tensor] = None, dx_sum: Optional[torch.Tensor] = None,
+                   side: Optional["torch.cuda.Stream"] = None) -> torch.Tensor:
     """Returns dx; writes every parameter gradient of the layer into the views ``gr``.
 
     ``dy_sum``: the column sums of ``dy`` when the kernel that produced ``dy`` already formed them
     (they are this block's FC2 bias gradient).  ``dx_sum``: a [d] tensor that receives the column
-    sums of the returned dx, for the block below."""
+    sums of the returned dx, for the block below.  ``side``: a second stream for the four
+    weight-gradient GEMMs, which nothing in the block's own backward chain depends on; they then
+    run beside the memory-bound kernels of the chain (GELU backward, layer-norm backward, the
+    q/k/v packing) instead of between them.  The current stream waits for ``side`` before the
+    function returns, and every tensor a side-stream GEMM reads stays referenced until then."""
     x, mean1, rstd1, h1, qd, kd, vd, att, a, x2, mean2, rstd2, h2, u, g = ctx
     T, d = x.shape
     S, H, dh = T // batch, cfg.n_head, cfg.head_dim
+    main = torch.cuda.current_stream(dy.device) if side is not None else None
+
+    def wgrad(dy_, x_, gw):
+        if side is None:
+            torch.mm(dy_.t(), x_, out=gw)
+            return
+        side.wait_stream(main)                  # dy_ and x_ are complete, gw's previous reader is done
+        with torch.cuda.stream(side):
+            torch.mm(dy_.t(), x_, out=gw)
+
     if dy_sum is not None:
         gr["fc2_b"].copy_(dy_sum)
-        _wgrad(dy, g, gr["fc2_w"], None)
     else:
-        _wgrad(dy, g, gr["fc2_w"], gr["fc2_b"])
+        _bias_grad(dy, gr["fc2_b"])
+    wgrad(dy, g, gr["fc2_w"])
     dg = torch.mm(dy, p["fc2_w"])
     du = _gelu_bwd(dg, u, gr["fc1_b"])
-    del dg
-    _wgrad(du, h2, gr["fc1_w"], None)
+    wgrad(du, h2, gr["fc1_w"])
     dh2 = torch.mm(du, p["fc1_w"])
-    del du
     # dx2 is the gradient of the attention projection's output: its column sums are proj_b's gradient
     dx2 = _ln_bwd(dh2, x2, mean2, rstd2, p["ln2_w"], p["ln2_b"], gr["ln2_w"], gr["ln2_b"], resid=dy, dx_sum=gr["proj_b"])
-    _wgrad(dx2, a, gr["proj_w"], None)
+    wgrad(dx2, a, gr["proj_w"])
     da = torch.mm(dx2, p["proj_w"])
     datt = da.view(batch, S, H, dh).transpose(1, 2)
     dq, dk, dv = torch.autograd.grad(att, (qd, kd, vd), datt)
     dqkv = _cat_qkv_grads(dq, dk, dv, T, d, gr["qkv_b"])
-    _wgrad(dqkv, h1, gr["qkv_w"], None)
+    wgrad(dqkv, h1, gr["qkv_w"])
     dh1 = torch.mm(dqkv, p["qkv_w"])
     dx = _ln_bwd(dh1, x, mean1, rstd1, p["ln1_w"], p["ln1_b"], gr["ln1_w"], gr["ln1_b"], resid=dx2, dx_sum=dx_sum)
+    if side is not None:
+        main.wait_stream(side)                  # the gradient buffer is complete for whoever reads it next
     return dx
 
 

@@ -95,7 +95,7 @@ class Zero3Engine:
     def __init__(self, cfg: GPTConfig, backend: Optional[TorchBackend] = None, optim: Optional[OptimConfig] = None,
                  device: Optional[torch.device] = None, seed: int = 1234, comm=None, group=None,
                  linear_fwd: Optional[Callable] = None, micro_batch: int = 1, fused_ag_gemm: bool = False,
-                 gather_ctas: int = 16, fused_gelu_gemm: bool = False):
+                 gather_ctas: int = 16, fused_gelu_gemm: bool = False, overlap_wgrad: bool = False):
         from .. import build_kernels
 
         self.C = build_kernels.load()
@@ -110,6 +110,9 @@ class Zero3Engine:
         self.linear_fwd = linear_fwd or gpt._default_linear
         # FC1 on the library's tcgen05 GEMM with bias and GELU in its epilogue (one kernel, two outputs)
         self.fused_gelu_gemm = bool(fused_gelu_gemm)
+        # weight-gradient GEMMs on a second stream, beside the memory-bound kernels of the backward chain
+        self.overlap_wgrad = bool(overlap_wgrad)
+        self._wgrad_stream = None
         self.micro_batch = micro_batch
         self.step_count = 0
         self.launches = 0          # kernels of this library launched by the last step
@@ -311,6 +314,11 @@ class Zero3Engine:
                                        self.loss_sum, self._ce, branch=branch, dx_sum=self._dx_sums[L % 2] if L > 0 else None)
         del branch
         # ---- backward through the blocks
+        wgrad_stream = None
+        if self.overlap_wgrad:
+            if self._wgrad_stream is None:
+                self._wgrad_stream = torch.cuda.Stream(device=self.device)
+            wgrad_stream = self._wgrad_stream
         for li in range(L, 0, -1):
             slot = li % 2
             _wait(nxt)
@@ -318,7 +326,8 @@ class Zero3Engine:
             gslot = li % 2
             _wait(self._rs_pending[gslot])          # the buffer's previous reduce-scatter has read it
             dx = gpt.layer_backward(dx, saved.pop(), self.pviews[li][slot], self.gviews[li][gslot], cfg, B,
-                                    dy_sum=self._dx_sums[li % 2], dx_sum=self._dx_sums[(li - 1) % 2] if li > 1 else None)
+                                    dy_sum=self._dx_sums[li % 2], dx_sum=self._dx_sums[(li - 1) % 2] if li > 1 else None,
+                                    side=wgrad_stream)
             self._rs_pending[gslot] = self._reduce(li, None if self.local_only else self.gradbuf[gslot])
         gpt.embed_backward(dx, tokens, self.gviews0)
         rs0 = self._reduce(0, self.gradbuf0)

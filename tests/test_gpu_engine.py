@@ -298,8 +298,8 @@ def test_gelu_forward_and_backward_with_bias_gradient(shape):
         torch.testing.assert_close(gb.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) + 1e-3)
 
 
-@pytest.mark.parametrize("fused_gelu_gemm", [False, True])
-def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm):
+@pytest.mark.parametrize("fused_gelu_gemm,overlap_wgrad", [(False, False), (True, False), (False, True)])
+def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm, overlap_wgrad):
     """A two-block model wide enough (d = 1024) for the fused add+layer-norm, layer-norm backward
     with residual, GELU and GELU-backward kernels, with FC1 optionally on the tcgen05 GEMM whose
     epilogue applies the GELU: loss and every gradient against torch autograd in fp32."""
@@ -311,13 +311,18 @@ def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm):
 
     init_distributed()
     cfg = GPTConfig(2, 1024, 8, 4096, vocab=2048, seq_len=128, name="gpt-test-1024")
-    engine = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=0.0, weight_decay=0.0), fused_gelu_gemm=fused_gelu_gemm)
+    engine = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=0.0, weight_decay=0.0), fused_gelu_gemm=fused_gelu_gemm,
+                         overlap_wgrad=overlap_wgrad)
     g = torch.Generator().manual_seed(11)
     toks = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=g).to(DEV)
     tokens, targets = toks[:, :-1].contiguous(), toks[:, 1:].contiguous()
     ref_loss, ref_params = _autograd_reference(cfg, engine, tokens, targets)
     before = gpt.native_launches
     loss = engine.train_step(tokens, targets)
+    if overlap_wgrad:
+        for _ in range(3):                              # repeated steps reuse the gradient buffers across streams
+            loss = engine.train_step(tokens, targets)
+        before = gpt.native_launches - (cfg.n_layer * 9 + 3)
     engine.check_errors()
     # per block: 2 ln_fwd, gelu or gemm_gelu, gelu_bwd, cat3, 2 x (ln_bwd + finalize); head: ln_fwd, ln_bwd + finalize
     assert gpt.native_launches - before == cfg.n_layer * 9 + 3
