@@ -15,7 +15,6 @@ from pathlib import Path
 from typing import Dict, List, Optional
 
 import torch
-import torch.distributed as dist
 
 ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:

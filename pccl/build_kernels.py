@@ -23,7 +23,7 @@ import importlib.util
 import os
 import sys
 from pathlib import Path
-from typing import List, Optional
+from typing import List
 
 _HERE = Path(__file__).resolve().parent
 CSRC = _HERE / "csrc"

@@ -18,7 +18,7 @@ the ``linear_fwd`` hook of ``LayerParams``.  The attention core uses
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Tuple
 
 import torch

@@ -10,7 +10,6 @@ GPUs): that is the baseline arm.
 """
 from __future__ import annotations
 
-import torch
 import torch.distributed as dist
 
 

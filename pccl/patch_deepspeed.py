@@ -23,12 +23,11 @@ from __future__ import annotations
 
 from typing import List, Optional
 
-import torch
 import torch.distributed as dist
 
 from .all_gather import all_gather_2D
 from .all_reduce import _all_reduce, barrier as _barrier, broadcast as _broadcast
-from .build_kernels import build, build_rank0_first
+from .build_kernels import build, build_rank0_first  # noqa: F401  (build: name kept from the reference module)
 from .process_groups import ProcessGroups
 from .reduce_scatter import reduce_scatter_2D
 
