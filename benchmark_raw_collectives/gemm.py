@@ -64,7 +64,7 @@ def main():
     rank, world, _ = init_distributed()
     dev = torch.device("cuda", torch.cuda.current_device())
     import pccl
-    from pccl.ops.ag_gemm import AllGatherLinear
+    from pccl.ops.ag_gemm import AllGatherLinear, auto_gather_ctas
 
     peaks = {}
     p = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
@@ -115,7 +115,8 @@ def main():
             t_link = remote / 770e9 * 1e3
             row = {"shape": name, "M": M, "N": N, "K": K, "P": world, "fused_ms": ms_ours, "nccl_plus_cublas_ms": ms_ref,
                    "roofline_ms": max(t_math, t_link), "frac_of_roofline": max(t_math, t_link) / ms_ours,
-                   "speedup_vs_baseline": ms_ref / ms_ours, "gather_ctas": args.gather_ctas, "cta_pair": not args.one_sm, "correct": bool(ok)}
+                   "speedup_vs_baseline": ms_ref / ms_ours, "gather_ctas": args.gather_ctas if args.gather_ctas > 0 else auto_gather_ctas(M, N, K, world),
+                   "cta_pair": not args.one_sm, "correct": bool(ok)}
             del lin
         rows.append(row)
         if rank == 0:

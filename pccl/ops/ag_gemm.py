@@ -13,6 +13,7 @@ that consumes the parameters starts only after it.
 """
 from __future__ import annotations
 
+import math
 from typing import Callable, Optional
 
 import torch
@@ -26,6 +27,23 @@ def _C():
     return build_kernels.load()
 
 
+def auto_gather_ctas(tokens: int, out_features: int, in_features: int, world: int, per_cta_gbs: float = 9.0,
+                     gemm_tflops: float = 1450.0, margin: float = 1.3) -> int:
+    """How many CTAs should move shards so that the gather just keeps ahead of the multiply.
+
+    The remote part of the weight, ``(P-1)/P * N * K`` bf16 elements, has to arrive within the
+    time the GEMM needs for the whole product; a gatherer CTA moves about ``per_cta_gbs`` GB/s
+    over NVLink while the other SMs multiply (9 GB/s measured inside this kernel at two ranks,
+    against 20-23 GB/s for the same copy path in a collective that has the GPU to itself), the
+    multiplying CTAs sustain about ``gemm_tflops`` together.  Every CTA that gathers is one that does not multiply, so the
+    count is the smallest even number that covers the required rate with ``margin``."""
+    remote_bytes = (world - 1) / world * out_features * in_features * 2
+    t_math = 2.0 * tokens * out_features * in_features / (gemm_tflops * 1e12)
+    need = remote_bytes / max(t_math, 1e-9) / (per_cta_gbs * 1e9) * margin
+    even = int(math.ceil(need / 2.0)) * 2
+    return max(4, min(32, even))
+
+
 class AllGatherLinear:
     def __init__(self, comm: Communicator, group: Optional[Group], out_features: int, in_features: int,
                  gather_ctas: int = 16, device=None, two_cta: bool = True):
@@ -37,7 +55,7 @@ class AllGatherLinear:
         if in_features % 8 != 0:
             raise ValueError("in_features must be a multiple of 8")
         self.N, self.K, self.P = out_features, in_features, P
-        self.gather_ctas = gather_ctas
+        self.gather_ctas = gather_ctas       # 0: sized per call from the shapes (auto_gather_ctas)
         self.two_cta = two_cta       # multiply with CTA pairs (cta_group::2, 256x256 tiles)
         self.w_shard = comm.empty((out_features // P, in_features), torch.bfloat16)
         dev = device or self.w_shard.device
@@ -46,8 +64,8 @@ class AllGatherLinear:
     def forward(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, check: bool = False) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.K)
-        y, err = _C().ag_gemm(self.comm.native, self.group.gid, x2, self.w_shard, self.w_full, bias, None,
-                              self.gather_ctas, self.two_cta)
+        g = self.gather_ctas if self.gather_ctas > 0 else auto_gather_ctas(x2.shape[0], self.N, self.K, self.P)
+        y, err = _C().ag_gemm(self.comm.native, self.group.gid, x2, self.w_shard, self.w_full, bias, None, g, self.two_cta)
         if check:
             code = int(err.item())
             self.comm.check(sync=False)
