@@ -111,13 +111,14 @@ def all_gather_2D(output_tensor: torch.Tensor, input_tensor: torch.Tensor, group
     if both_native and _hier_native_fits(inner.comm, output_tensor, input_tensor, intra * inter):
         return _all_gather_2d_native(output_tensor, input_tensor, inner, outer, intra, inter, async_op,
                                      algo_from_flags(algorithm, use_rd), lanes)
-    assert not async_op, "Non blocking version not implemented for mixed backends"
+    # Mixed or non-native levels: two blocking calls.  The reference refuses async_op here
+    # (pccl/all_gather.py:143); this path runs in order and hands back a request that is already complete.
     intermediate = torch.empty(input_tensor.size(0) * inter, device=input_tensor.device, dtype=input_tensor.dtype)
     _all_gather(intermediate, input_tensor, outer, False, use_rd, use_pccl_cpp_backend, algorithm, lanes)
     _all_gather(output_tensor, intermediate, inner, False, use_rd, use_pccl_cpp_backend, algorithm, lanes)
     # inner-major -> global-rank order
     output_tensor.copy_(output_tensor.view(intra, inter, -1).transpose(0, 1).reshape(-1))
-    return None
+    return completed_request() if async_op else None
 
 
 def _hier_native_fits(comm, out: torch.Tensor, inp: torch.Tensor, total_ranks: int) -> bool:

@@ -123,14 +123,15 @@ def reduce_scatter_2D(output_tensor: torch.Tensor, input_tensor: torch.Tensor, g
     if both_native and _hier_fits(inner.comm, input_tensor, n, intra, inter):
         return _reduce_scatter_2d_native(output_tensor, input_tensor, inner, outer, intra, inter, n, async_op,
                                          algo_from_flags(algorithm, use_rh), scale, lanes)
-    assert not async_op, "Non blocking version not implemented for mixed backends"
+    # Mixed or non-native levels: two blocking calls.  The reference refuses async_op here
+    # (pccl/reduce_scatter.py:212); this path runs in order and hands back a request that is already complete.
     # [outer][inner][n] -> [inner][outer][n] so that the inner level scatters contiguous blocks
     permuted = input_tensor.view(inter, intra, -1).transpose(0, 1).reshape(-1)
     intermediate = torch.empty(input_tensor.numel() // intra, device=input_tensor.device, dtype=input_tensor.dtype)
     _reduce_scatter(intermediate, permuted, inner, False, False, use_rh, use_pccl_cpp_backend, algorithm, lanes=lanes)
     _reduce_scatter(output_tensor, intermediate, outer, False, False, use_rh, use_pccl_cpp_backend, algorithm,
                     scale=scale, lanes=lanes)
-    return None
+    return completed_request() if async_op else None
 
 
 def _hier_fits(comm, inp: torch.Tensor, n: int, intra: int, inter: int) -> bool:

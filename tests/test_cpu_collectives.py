@@ -158,3 +158,61 @@ def _dead_peer(rank, world):
 
 def test_missing_rank_times_out(port):
     run_ranks(_dead_peer, 2, port)
+
+
+def _patched_backend(rank, world):
+    """patch_deepspeed on CPU ranks: the five backend methods go through the 2-D library path for
+    world-sized groups and SUM, and fall back to the saved originals otherwise."""
+    import pccl  # noqa: F401
+    from pccl import patch_deepspeed as pd
+    from pccl.parallel.backend import TorchBackend
+
+    be = TorchBackend()
+    pgs = pd.patch_deepspeed(2, algorithm=None)            # 2 x 2 grid; reference choice: recursive variants
+    assert pd.get_heir_pg() is pgs and pgs.get_world_size() == [2, 2]
+    for name in ("all_gather_into_tensor", "reduce_scatter_tensor", "all_reduce", "broadcast", "barrier"):
+        assert hasattr(TorchBackend, "old_" + name)
+    assert TorchBackend.fused_scale and TorchBackend.symmetric_memory
+    assert pd.is_global_pg(None) and pd.is_global_pg(dist.group.WORLD)
+    gen = torch.Generator().manual_seed(99 + rank)
+    n = 1000
+    x = torch.randn(n, generator=gen)
+    out, gold = torch.empty(world * n), torch.empty(world * n)
+    assert be.all_gather_into_tensor(out, x) is None       # global-rank order although the grid is 2-D
+    be.old_all_gather_into_tensor(gold, x)
+    assert torch.equal(out, gold)
+    big = torch.randn(world * n, generator=gen)
+    out, gold = torch.empty(n), torch.empty(n)
+    be.reduce_scatter_tensor(out, big, scale=0.25)
+    be.old_reduce_scatter_tensor(gold, big)
+    torch.testing.assert_close(out, gold * 0.25, rtol=1e-5, atol=1e-6)
+    t = torch.randn(n + 1, generator=gen)
+    ref = t.clone()
+    be.all_reduce(t)
+    be.old_all_reduce(ref)
+    torch.testing.assert_close(t, ref, rtol=1e-5, atol=1e-6)
+    b = torch.full((5,), float(rank))
+    be.broadcast(b, 3)
+    assert torch.equal(b, torch.full((5,), 3.0))
+    be.barrier()
+    # not the whole world, or not a sum: the original methods run
+    sub = dist.new_group([0, 1])
+    if rank < 2:
+        o2 = torch.empty(2 * n)
+        be.all_gather_into_tensor(o2, x, group=sub)
+        g2 = torch.empty(2 * n)
+        dist.all_gather_into_tensor(g2, x, group=sub)
+        assert torch.equal(o2, g2)
+    m = torch.full((3,), float(rank))
+    be.all_reduce(m, op=dist.ReduceOp.MAX)
+    assert torch.equal(m, torch.full((3,), float(world - 1)))
+    req = be.all_gather_into_tensor(out := torch.empty(world * n), x, async_op=True)
+    req.wait()
+    be.old_all_gather_into_tensor(gold := torch.empty(world * n), x)
+    assert torch.equal(out, gold)
+    pd.unpatch_deepspeed()
+    assert not hasattr(TorchBackend, "old_all_reduce") and not TorchBackend.fused_scale
+
+
+def test_patched_backend_world4_on_cpu(port):
+    run_ranks(_patched_backend, 4, port)

@@ -162,3 +162,84 @@ def test_layer_math_fallback_matches_autograd_on_cpu():
         y, _ctx = gpt.layer_forward(x0, params[1], cfg, B)
         x2, m, _ctx = gpt.layer_forward_deferred(x0, None, params[1], cfg, B)
     torch.testing.assert_close(y, x2 + m)
+
+
+def test_clock_sampler_reads_a_fake_nvml(monkeypatch):
+    """The sampler only reads: SM clock, power and the clock-event reasons, through whatever
+    NVML binding is importable.  A stand-in module plays the device."""
+    import sys
+    import time
+    import types
+
+    from pccl.utils.clocks import ClockSampler
+
+    calls = {"set": 0}
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    fake.nvmlInit = lambda: None
+    fake.nvmlDeviceGetHandleByIndex = lambda i: ("gpu", i)
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, which: 1965
+    clocks = iter([1900, 1600, 1500, 1605] + [1605] * 1000)
+    fake.nvmlDeviceGetClockInfo = lambda h, which: next(clocks)
+    fake.nvmlDeviceGetPowerUsage = lambda h: 987000            # milliwatts
+    fake.nvmlDeviceGetCurrentClocksEventReasons = lambda h: 0x4   # sw_power_cap
+
+    def forbidden(*a, **k):                                   # any setter would be a bug
+        calls["set"] += 1
+        raise AssertionError("the sampler must not change device settings")
+
+    for name in ("nvmlDeviceSetApplicationsClocks", "nvmlDeviceSetGpuLockedClocks", "nvmlDeviceResetGpuLockedClocks",
+                 "nvmlDeviceSetPowerManagementLimit", "nvmlDeviceSetPersistenceMode"):
+        setattr(fake, name, forbidden)
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    s = ClockSampler(3, period_s=0.005).start()
+    time.sleep(0.08)
+    out = s.stop()
+    assert calls["set"] == 0
+    assert out["sm_max_mhz"] == 1965 and out["samples"] >= 4
+    assert out["reasons"] == ["sw_power_cap"] and out["power_w_max"] == 987.0
+    assert 1500 <= out["sm_mhz"] <= 1900
+    assert ClockSampler(0).summary() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+
+
+def test_benchmark_helpers(tmp_path, monkeypatch):
+    from benchmark_raw_collectives import utils as bu
+
+    assert bu.parse_sizes("1M, 64m,1G,512", []) == [1 << 20, 64 << 20, 1 << 30, 512]
+    assert bu.parse_sizes(None, [7]) == [7]
+    assert bu.sizes_pow2(1 << 20, 1 << 23) == [1 << 20, 1 << 21, 1 << 22, 1 << 23]
+    # 8 ranks, 1 GiB each, 10 ms: (P-1) * bytes / time
+    assert bu.bus_bandwidth_gbs(1 << 30, 8, 10.0) == pytest.approx(7 * (1 << 30) / 0.010 / 1e9)
+    assert bu.bus_bandwidth_gbs(1 << 30, 1, 10.0) == 0.0
+    x = torch.arange(1000, dtype=torch.float32)
+    y = x.clone()
+    y[:15] += 1.0                                             # 1.5 % of the elements differ: within the 2 % rule
+    assert bu.allclose(x, y)
+    y[:30] += 1.0
+    assert not bu.allclose(x, y)
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("SLURM_JOB_ID", "4242")
+    log = bu.CsvLog("all_gather", "b200", 8, ["gpu_count", "output_size", "time_pccl"], enabled=True)
+    log.row({"gpu_count": 8, "output_size": 64, "time_pccl": 0.5, "ignored": 1})
+    log.fh.close()
+    text = (tmp_path / "data" / "all_gather" / "b200" / "gpus_8_slurm_4242.csv").read_text().splitlines()
+    assert text == ["gpu_count,output_size,time_pccl", "8,64,0.5"]
+    bu.CsvLog("x", "y", 1, ["a"], enabled=False).row({"a": 1})   # disabled: no file, no error
+    assert not (tmp_path / "data" / "x").exists()
+
+
+def test_gatherer_count_follows_the_required_rate():
+    from pccl.ops.ag_gemm import auto_gather_ctas
+
+    # fewer tokens per weight byte -> the gather must run faster -> more gatherers; always even, 4..32
+    few = auto_gather_ctas(8192, 6144, 2048, 2)
+    more = auto_gather_ctas(4096, 12288, 4096, 2)
+    assert few < more
+    for P in (2, 4, 8):
+        for M in (1024, 4096, 8192, 65536):
+            g = auto_gather_ctas(M, 8192, 2048, P)
+            assert g % 2 == 0 and 4 <= g <= 32
+    assert auto_gather_ctas(8192, 6144, 2048, 8) >= auto_gather_ctas(8192, 6144, 2048, 2)
+    assert auto_gather_ctas(1 << 20, 8192, 2048, 8) == 4      # plenty of math per byte: the minimum
+    # the width of the layer cancels: both the bytes and the FLOPs scale with it
+    assert auto_gather_ctas(4096, 4096, 4096, 4) == auto_gather_ctas(4096, 16384, 4096, 4)
