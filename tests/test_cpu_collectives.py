@@ -216,3 +216,37 @@ def _patched_backend(rank, world):
 
 def test_patched_backend_world4_on_cpu(port):
     run_ranks(_patched_backend, 4, port)
+
+
+def _fd_channel_and_max(rank, world):
+    """The bootstrap's descriptor channel (unix datagram sockets, SCM_RIGHTS) with ordinary
+    files standing in for exported GPU allocations, and the max-over-ranks reduction."""
+    import os
+    import tempfile
+
+    from pccl.comm import _FdChannel
+    from pccl.utils.timing import max_over_ranks
+
+    job = f"test{os.environ['MASTER_PORT']}"
+    ch = _FdChannel(job, rank, world, timeout_s=20.0)
+    dist.barrier()                                         # every socket is bound before anyone sends
+    with tempfile.TemporaryFile() as f:
+        f.write(f"heap of rank {rank}".encode())
+        f.flush()
+        for dst in range(world):
+            if dst != rank:
+                ch.send(dst, [os.dup(f.fileno())], tag=7)  # send() closes the descriptors it was given
+        got = {}
+        for _ in range(world - 1):
+            src, tag, fds = ch.recv()
+            assert tag == 7 and len(fds) == 1
+            with os.fdopen(fds[0], "rb") as peer:
+                peer.seek(0)
+                got[src] = peer.read().decode()
+    assert got == {r: f"heap of rank {r}" for r in range(world) if r != rank}
+    ch.close()
+    assert max_over_ranks(10.0 + rank) == 10.0 + world - 1
+
+
+def test_descriptor_channel_and_max_over_ranks(port):
+    run_ranks(_fd_channel_and_max, 3, port)
