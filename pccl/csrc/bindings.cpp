@@ -483,6 +483,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("multicast_release", &VmmSegment::multicast_release)
       .def("close", &VmmSegment::close);
 
+  py::class_<OffsetAllocator>(m, "OffsetAllocator",
+                              "first-fit allocator over byte offsets: the bookkeeping of the symmetric heap (no device memory involved)")
+      .def(py::init<uint64_t>(), py::arg("size"))
+      .def("alloc", &OffsetAllocator::alloc, py::arg("bytes"), py::arg("align") = 256, "offset, or -1 when it does not fit")
+      .def("free", &OffsetAllocator::free, py::arg("offset"))
+      .def_property_readonly("used", &OffsetAllocator::used)
+      .def_property_readonly("size", &OffsetAllocator::size)
+      .def("largest_free", &OffsetAllocator::largest_free);
+
   py::class_<Comm, std::shared_ptr<Comm>>(m, "Comm")
       .def(py::init<int, int, int, int, std::vector<uint64_t>, std::vector<uint64_t>, uint64_t, uint64_t, uint64_t, uint64_t>(),
            py::arg("world"), py::arg("rank"), py::arg("nlocal"), py::arg("device"), py::arg("heaps"), py::arg("sigs"),

@@ -243,3 +243,43 @@ def test_gatherer_count_follows_the_required_rate():
     assert auto_gather_ctas(1 << 20, 8192, 2048, 8) == 4      # plenty of math per byte: the minimum
     # the width of the layer cancels: both the bytes and the FLOPs scale with it
     assert auto_gather_ctas(4096, 4096, 4096, 4) == auto_gather_ctas(4096, 16384, 4096, 4)
+
+
+def test_offset_allocator_random_sequences():
+    """The symmetric heap's bookkeeping: blocks never overlap, honour their alignment, the
+    byte count is exact, freed neighbours merge, and a drained heap is one free range again."""
+    import random
+
+    import pccl
+
+    A = pccl._C.OffsetAllocator
+    rng = random.Random(5)
+    for trial in range(20):
+        size = rng.choice([1 << 16, 1 << 20, (1 << 20) + 12345])
+        a = A(size)
+        live = {}
+        for _ in range(400):
+            if live and rng.random() < 0.45:
+                off = rng.choice(list(live))
+                a.free(off)
+                del live[off]
+            else:
+                nbytes = rng.choice([1, 7, 256, 4096, rng.randrange(1, size // 8)])
+                align = rng.choice([1, 16, 256, 4096])
+                off = a.alloc(nbytes, align)
+                if off < 0:
+                    assert a.largest_free() < nbytes + align     # refusal only when it truly cannot fit aligned
+                    continue
+                assert off % align == 0 and off + nbytes <= size
+                for o, n in live.items():
+                    assert off + nbytes <= o or o + n <= off, "blocks overlap"
+                live[off] = nbytes
+            assert a.used == sum(live.values())
+        for off in list(live):
+            a.free(off)
+        assert a.used == 0 and a.largest_free() == size
+    a = A(1024)
+    assert a.alloc(0, 0) == 0                       # zero bytes still gets a distinct offset
+    assert a.alloc(2048, 1) == -1
+    with pytest.raises(RuntimeError):
+        a.free(512)                                 # never allocated
