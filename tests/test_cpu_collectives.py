@@ -240,9 +240,9 @@ def _fd_channel_and_max(rank, world):
         for _ in range(world - 1):
             src, tag, fds = ch.recv()
             assert tag == 7 and len(fds) == 1
-            with os.fdopen(fds[0], "rb") as peer:
-                peer.seek(0)
-                got[src] = peer.read().decode()
+            # positional read: the received descriptor shares its file offset with the sender's
+            got[src] = os.pread(fds[0], 100, 0).decode()
+            os.close(fds[0])
     assert got == {r: f"heap of rank {r}" for r in range(world) if r != rank}
     ch.close()
     assert max_over_ranks(10.0 + rank) == 10.0 + world - 1
