@@ -77,7 +77,10 @@ void ce_fwd_bwd(at::Tensor& logits, const at::Tensor& targets, at::Tensor& loss_
                               at::cuda::getCurrentCUDAStream().stream()));
 }
 
-// Scratch that lives as long as the process: one buffer per device, grown on demand.
+// Scratch that lives as long as the process: one buffer per device, grown on demand.  The
+// column-sum family uses the front of it and the layer-norm backward the rest, so launches of
+// the same family must be ordered with each other on the device (the engine issues them on
+// one stream); two of them running at once on different streams would share partial sums.
 at::Tensor& scratch(int device, int64_t floats) {
   static at::Tensor bufs[64];
   at::Tensor& b = bufs[device & 63];
