@@ -283,3 +283,31 @@ def test_offset_allocator_random_sequences():
     assert a.alloc(2048, 1) == -1
     with pytest.raises(RuntimeError):
         a.free(512)                                 # never allocated
+
+
+def test_committed_tuning_table_is_well_formed():
+    """Every row names known variants, thresholds ascend and end open, lanes fit the kernels'
+    flag layout, and for every measured group size the last preference of every row needs
+    neither NVLS nor symmetric input (so `auto` always has something it may run)."""
+    import json
+
+    table = json.loads(tuner.TABLE_PATH.read_text())
+    assert {"all_gather", "reduce_scatter", "all_reduce"} <= set(table)
+    for coll, by_world in table.items():
+        if coll.startswith("_"):
+            continue
+        for world, rows in by_world.items():
+            assert int(world) in (2, 4, 8)
+            assert rows and rows[-1][0] is None, f"{coll} P={world}: the last row must be open-ended"
+            limits = [r[0] for r in rows[:-1]]
+            assert limits == sorted(limits) and all(isinstance(x, int) and x > 0 for x in limits)
+            for _limit, algos, lanes in rows:
+                algos = [algos] if isinstance(algos, str) else algos
+                assert algos and all(a in sch.ALGO_IDS for a in algos)
+                assert 1 <= int(lanes) <= 160
+            # whatever the tensors look like, something feasible comes out
+            for nbytes in (1 << 10, 1 << 20, 1 << 24, 1 << 30):
+                algo, nl = tuner.choose(coll, int(world), nbytes, symmetric_in=False, symmetric_out=False, has_multimem=False)
+                assert algo in sch.ALGO_IDS and algo not in (sch.MULTIMEM,) and nl >= 1
+                if coll == "reduce_scatter":
+                    assert algo != sch.PULL         # pull reads the peers' inputs: they must be symmetric
