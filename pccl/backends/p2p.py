@@ -29,17 +29,19 @@ def _exchange(send: Optional[torch.Tensor], dst_global: int, recv: Optional[torc
         ops.append(dist.P2POp(dist.irecv, recv, src_global, group=pg))
     if not ops:
         return
-    works = dist.batch_isend_irecv(ops)
-    for w in works:
-        try:
+    # gloo/NCCL report an expired wait as RuntimeError, and a peer whose process has already gone
+    # as RuntimeError too ("connection closed by peer"), sometimes while the operation is being posted
+    try:
+        works = dist.batch_isend_irecv(ops)
+        for w in works:
             if timeout_s is None:
                 w.wait()
             else:
                 w.wait(datetime.timedelta(seconds=timeout_s))
-        except RuntimeError as exc:  # gloo/NCCL report an expired wait as RuntimeError
-            raise PcclTimeoutError(
-                f"p2p step with dst={dst_global} src={src_global} did not complete: {exc}"
-            ) from exc
+    except RuntimeError as exc:
+        raise PcclTimeoutError(
+            f"p2p step with dst={dst_global} src={src_global} did not complete: {exc}"
+        ) from exc
 
 
 class P2PTransport:
