@@ -3,7 +3,8 @@
 Command line of ``benchmark_raw_collectives/all_gather.py`` in the reference
 (``--num-gpus-per-node --machine --library {pccl,mpi,xccl} --pccl-disable-cpp-backend
 --test --pccl-recursive-alg --dtype``), plus ``--algorithm``, ``--sizes``, ``--size-mode``,
-``--symmetric`` and ``--json``.  ``--library xccl`` (also spelled ``rccl`` / ``nccl``) is the
+``--symmetric``, ``--nvls``, ``--json``, ``--write-tuning-table`` and ``--impl reference`` (which hands
+over to ``baseline/run_reference.py``: the unmodified reference on its NCCL branch).  ``--library xccl`` (also spelled ``rccl`` / ``nccl``) is the
 reference's NCCL path, ``dist.all_gather_into_tensor`` on the world group; ``mpi`` is not
 available here (no MPI implementation) and is refused.
 
@@ -30,7 +31,7 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 from benchmark_raw_collectives.utils import (NVLINK_GBS_NOMINAL, CsvLog, allclose, bus_bandwidth_gbs, init,  # noqa: E402
-                                             parse_sizes, sizes_pow2, time_something)
+                                             parse_sizes, sizes_pow2, time_something, update_tuning_table)
 
 
 def main() -> None:
@@ -51,7 +52,16 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", type=str, default=None, help="write all rows to this file (rank 0)")
+    ap.add_argument("--nvls", type=int, default=None, help="1: bind an NVLS multicast mapping (multimem variant)")
+    ap.add_argument("--write-tuning-table", type=str, default=None, metavar="PATH",
+                    help="with --algorithm all: replace this group size's all-gather rows of the tuner's table")
+    ap.add_argument("--impl", type=str, default="pccl", choices=["pccl", "reference"],
+                    help="reference: run the unmodified reference benchmark (its --library xccl branch) instead")
     args = ap.parse_args()
+    if args.impl == "reference":
+        runner = str(Path(__file__).resolve().parent.parent / "baseline" / "run_reference.py")
+        cmd = [sys.executable, runner, "all_gather", "--dtype", args.dtype] + (["--json", args.json] if args.json else [])
+        os.execv(sys.executable, cmd)
     if args.library == "mpi":
         raise SystemExit("--library mpi: no MPI implementation is installed on this machine")
 
@@ -75,7 +85,8 @@ def main() -> None:
 
         build_kernels.build_rank0_first(dist.barrier)     # rank 0 compiles first, like the reference's callers
         heap = (world + 1) * max_in + (256 << 20) + (64 << 20) if args.symmetric else (512 << 20)
-        comm = pccl.init(heap_bytes=heap, staging_bytes=256 << 20)
+        comm = pccl.init(heap_bytes=heap, staging_bytes=256 << 20,
+                         enable_nvls=None if args.nvls is None else bool(args.nvls))
         pgs = pccl.ProcessGroups(args.num_gpus_per_node, world // args.num_gpus_per_node)
         group = pgs.get_flat_group()
     if args.algorithm == "all":
@@ -142,6 +153,13 @@ def main() -> None:
     if args.json and rank == 0:
         Path(args.json).parent.mkdir(parents=True, exist_ok=True)
         Path(args.json).write_text(json.dumps(rows, indent=1))
+    if args.write_tuning_table and rank == 0 and not baseline and len(algos) > 1:
+        pts = {}
+        for r in rows:
+            pt = pts.setdefault(r["per_rank_bytes"], {"collective": "all_gather", "P": world,
+                                                      "per_rank_bytes": r["per_rank_bytes"], "variants": {}})
+            pt["variants"][r["algorithm"]] = {"ms": r["time_ms"]}
+        update_tuning_table(Path(args.write_tuning_table), "all_gather", world, list(pts.values()))
     dist.barrier()
     if comm is not None:
         pccl.shutdown()

@@ -1,13 +1,16 @@
 """Reduce-scatter (SUM) bandwidth sweep and correctness check.
 
 Command line of ``benchmark_raw_collectives/reduce_scatter.py`` in the reference, plus
-``--algorithm``, ``--sizes``, ``--dtype``, ``--out-dtype``, ``--symmetric`` and ``--json``.  Unlike
+``--algorithm``, ``--sizes``, ``--size-mode``, ``--dtype``, ``--out-dtype``, ``--symmetric``, ``--nvls``,
+``--json``, ``--write-tuning-table`` and ``--impl reference`` (hands over to
+``baseline/run_reference.py``: the unmodified reference on its NCCL branch).  Unlike
 the reference (which always passes ``use_rh=True`` whatever the flag says, line 95), the
 algorithm flag is respected.  ``--library xccl|rccl|nccl`` is ``dist.reduce_scatter_tensor``
 on the world group.
 
-Sizes are the PER-RANK INPUT buffer (default bf16, 8 MiB..1 GiB; the top of the range can be
-raised with ``--sizes`` up to what the heap holds); every rank's result is input / world.
+Sizes are the PER-RANK INPUT buffer (default bf16, 8 MiB..8 GiB); every rank's result is
+input / world.  The reference's own sweep is ``--dtype fp32 --sizes 1M,2M,...,1G`` (it calls the
+same quantity the total input, ``benchmark_raw_collectives/reduce_scatter.py:86-90``).
 bf16 inputs are summed with fp32 accumulation.  Times are device-timed, maximum over ranks;
 bus bandwidth = (P-1)/P * input bytes / time.
 
@@ -28,7 +31,7 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 from benchmark_raw_collectives.utils import (NVLINK_GBS_NOMINAL, CsvLog, init, parse_sizes, sizes_pow2,  # noqa: E402
-                                             time_something)
+                                             time_something, update_tuning_table)
 
 
 def main() -> None:
@@ -48,7 +51,18 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", type=str, default=None)
+    ap.add_argument("--size-mode", type=str, default="input", choices=["input", "output"],
+                    help="input: sizes are each rank's INPUT buffer (what the reference calls the total input); "
+                         "output: sizes are the per-rank result, the input is world times larger")
+    ap.add_argument("--nvls", type=int, default=None, help="1: bind an NVLS multicast mapping (multimem variant)")
+    ap.add_argument("--write-tuning-table", type=str, default=None, metavar="PATH",
+                    help="with --algorithm all: replace this group size's reduce-scatter rows of the tuner's table")
+    ap.add_argument("--impl", type=str, default="pccl", choices=["pccl", "reference"],
+                    help="reference: run the unmodified reference benchmark (its NCCL branch; fp32, total input 1..1024 MiB)")
     args = ap.parse_args()
+    if args.impl == "reference":
+        runner = str(Path(__file__).resolve().parent.parent / "baseline" / "run_reference.py")
+        os.execv(sys.executable, [sys.executable, runner, "reduce_scatter"] + (["--json", args.json] if args.json else []))
     if args.library == "mpi":
         raise SystemExit("--library mpi: no MPI implementation is installed on this machine")
 
@@ -60,7 +74,9 @@ def main() -> None:
     baseline = args.library in ("xccl", "rccl", "nccl")
     if baseline:
         out_dtype = dtype
-    sizes = parse_sizes(args.sizes, sizes_pow2(8 << 20, 1 << 30))
+    sizes = parse_sizes(args.sizes, sizes_pow2(8 << 20, 8 << 30))
+    if args.size_mode == "output":
+        sizes = [s * world for s in sizes]
     max_in = max(sizes)
 
     import pccl
@@ -73,7 +89,7 @@ def main() -> None:
         build_kernels.build_rank0_first(dist.barrier)
         staging = max(256 << 20, max_in)             # push variants stage (P-1)/P of the input
         heap = (max_in + (64 << 20) if args.symmetric else (64 << 20)) + staging + (64 << 20)
-        comm = pccl.init(heap_bytes=heap, staging_bytes=staging)
+        comm = pccl.init(heap_bytes=heap, staging_bytes=staging, enable_nvls=None if args.nvls is None else bool(args.nvls))
         pgs = pccl.ProcessGroups(args.num_gpus_per_node, world // args.num_gpus_per_node)
         group = pgs.get_flat_group()
     if args.algorithm == "all":
@@ -148,6 +164,13 @@ def main() -> None:
     if args.json and rank == 0:
         Path(args.json).parent.mkdir(parents=True, exist_ok=True)
         Path(args.json).write_text(json.dumps(rows, indent=1))
+    if args.write_tuning_table and rank == 0 and not baseline and len(algos) > 1:
+        pts = {}
+        for r in rows:
+            pt = pts.setdefault(r["per_rank_bytes"], {"collective": "reduce_scatter", "P": world,
+                                                      "per_rank_bytes": r["per_rank_bytes"], "variants": {}})
+            pt["variants"][r["algorithm"]] = {"ms": r["time_ms"]}
+        update_tuning_table(Path(args.write_tuning_table), "reduce_scatter", world, list(pts.values()))
     dist.barrier()
     if comm is not None:
         pccl.shutdown()

@@ -98,3 +98,53 @@ class CsvLog:
         if self.enabled:
             self.w.writerow([values.get(c, "") for c in self.columns])
             self.fh.flush()
+
+
+def tuning_rows(points: List[Dict]) -> List[List]:
+    """Turn measured points of one collective and group size into rows of the tuner's table.
+
+    ``points``: dictionaries with ``per_rank_bytes``, the tuner's key (all-gather: bytes each rank
+    contributes; reduce-scatter: bytes of the per-rank INPUT BUFFER, converted here to the result
+    block the tuner is asked about) and ``variants`` = {name: {"ms": ...}}.  For every size the
+    preference list is: the fastest variant, then the fastest one that needs no multicast mapping,
+    then ``direct`` (which every tensor placement can run).  Neighbouring sizes with the same list
+    share a row; a row covers sizes up to and including its ``max_bytes``, the last one everything
+    above."""
+    pts = sorted(points, key=lambda p: p["per_rank_bytes"])
+    rows: List[List] = []
+    for p in pts:
+        order = sorted(p["variants"], key=lambda a: p["variants"][a]["ms"])
+        prefs = [order[0]]
+        plain = [a for a in order if a != "multimem"]
+        if plain and plain[0] not in prefs:
+            prefs.append(plain[0])
+        if "direct" not in prefs:
+            prefs.append("direct")
+        key_bytes = p["per_rank_bytes"]
+        if p["collective"] == "reduce_scatter":
+            key_bytes //= p["P"]
+        lanes = 32 if key_bytes <= (4 << 20) else 64
+        if rows and rows[-1][1] == prefs and rows[-1][2] == lanes:
+            rows[-1][0] = key_bytes
+        else:
+            rows.append([key_bytes, prefs, lanes])
+    if rows:
+        rows[-1][0] = None
+    return rows
+
+
+def update_tuning_table(path: Path, collective: str, world: int, points: List[Dict]) -> None:
+    """Replace the rows of (collective, world) in the JSON table at ``path`` with the winners of
+    ``points``; everything else in the file is kept."""
+    import json
+
+    table: Dict = {}
+    if path.exists():
+        try:
+            table = json.loads(path.read_text())
+        except ValueError:
+            table = {}
+    table.setdefault(collective, {})[str(world)] = tuning_rows(points)
+    table["_comment"] = ("size x group -> preferred variants (first feasible wins) and lanes; written by "
+                         "benchmark_raw_collectives/sweep.py --write-tuning-table from device-timed, max-over-ranks times")
+    path.write_text(json.dumps(table, indent=1) + "\n")

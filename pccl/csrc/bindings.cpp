@@ -210,6 +210,13 @@ void reduce_scatter(Comm& c, int gid, std::vector<at::Tensor> outs, std::vector<
   const uint64_t n = (uint64_t)outs[0].numel();
   if (n == 0) return;
   cudaStream_t stream = current_stream(dev);
+  if (P == 1 && tin == tout && scale == 1.0) {
+    // A group of one with nothing to scale or convert: the result is the input, and the copy
+    // engine moves it without occupying an SM (as the one-rank all-gather does).
+    if (outs[0].data_ptr() != ins[0].data_ptr())
+      PCCL_CUDA(cudaMemcpyAsync(outs[0].data_ptr(), ins[0].data_ptr(), outs[0].nbytes(), cudaMemcpyDeviceToDevice, stream));
+    return;
+  }
   const int64_t in_off = symmetric_offset(c, gid, l, ins);
   const uint64_t si = dtype_size(tin), sw = dtype_size(tw), so = dtype_size(tout);
 

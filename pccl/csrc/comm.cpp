@@ -82,6 +82,7 @@ Comm::Comm(int world, int rank, int nlocal, int device, std::vector<uint64_t> he
   std::memset(status_, 0, sizeof(Status) * nlocal);
   PCCL_CUDA(cudaMalloc((void**)&poison_, sizeof(uint32_t) * nlocal));
   PCCL_CUDA(cudaMemset(poison_, 0, sizeof(uint32_t) * nlocal));
+  PCCL_CUDA(cudaEventCreateWithFlags(&staging_tail_, cudaEventDisableTiming));
   max_lanes_ = max_resident_lanes(device);
   if (max_lanes_ <= 0) throw Error("could not determine how many lanes fit on the device");
   if (staging_bytes > 0) {
@@ -95,6 +96,7 @@ Comm::Comm(int world, int rank, int nlocal, int device, std::vector<uint64_t> he
 Comm::~Comm() {
   for (auto& g : groups_)
     if (g.tail) cudaEventDestroy(g.tail);
+  if (staging_tail_) cudaEventDestroy(staging_tail_);
   if (status_) cudaFreeHost(status_);
   if (poison_) cudaFree(poison_);
   if (trace_) cudaFree(trace_);
@@ -205,9 +207,21 @@ void Comm::reset_after_failure() {
   PCCL_CUDA(cudaDeviceSynchronize());
 }
 
-void Comm::begin_call(int gid, GroupDev* g, cudaStream_t stream) {
+void Comm::begin_call(int gid, GroupDev* g, cudaStream_t stream, bool uses_staging) {
   GroupState& gs = groups_.at(gid);
   if (gs.my_index < 0) throw Error("this rank is not a member of the group");
+  // The staging area belongs to the communicator, not to a group: two launches that use it must
+  // not overlap on this rank even when they belong to different groups (whose flags are
+  // separate) and sit on different streams.  A peer writes into this rank's staging only after
+  // this rank's kernel of the same call has signalled its entry, so local ordering is enough.
+  if (uses_staging) {
+    if (staging_used_ && staging_stream_ != stream) {
+      PCCL_CUDA(cudaEventRecord(staging_tail_, staging_stream_));
+      PCCL_CUDA(cudaStreamWaitEvent(stream, staging_tail_, 0));
+    }
+    staging_used_ = true;
+    staging_stream_ = stream;
+  }
   // Calls on one group share its flags, so they must execute in issue order even when the
   // caller switches streams.
   if (gs.used && gs.last_stream != stream) {
@@ -254,27 +268,31 @@ int Comm::clamp_lanes(int nlanes, const GroupState& gs) const {
 void Comm::all_gather(int gid, AllGatherArgs a, int nlanes, cudaStream_t stream) {
   if (a.algo == kMultimem && mc_heap_ == 0) throw Error("multimem all-gather requested but no multicast mapping exists");
   if (a.algo == kRecursive && !is_pow2(group_size(gid))) throw Error("recursive doubling needs a power-of-two group");
-  begin_call(gid, &a.g, stream);
+  // user tensors never lie inside the staging area (the allocator has reserved it), so an offset
+  // there means staging; pull leaves recv_off unused and stages only a private input
+  const bool staged = a.algo == kPull ? (a.in[0] != nullptr || in_staging(a.in_off)) : in_staging(a.recv_off);
+  begin_call(gid, &a.g, stream, staged);
   PCCL_CUDA(launch_all_gather(a, clamp_lanes(nlanes, groups_[gid]), stream));
 }
 
 void Comm::reduce_scatter(int gid, ReduceScatterArgs a, int nlanes, cudaStream_t stream) {
   if (a.algo == kMultimem && mc_heap_ == 0) throw Error("multimem reduce-scatter requested but no multicast mapping exists");
   if (a.algo == kRecursive && !is_pow2(group_size(gid))) throw Error("recursive halving needs a power-of-two group");
-  begin_call(gid, &a.g, stream);
+  const bool staged = a.algo != kPull && a.algo != kMultimem && in_staging(a.stage_off);
+  begin_call(gid, &a.g, stream, staged);
   PCCL_CUDA(launch_reduce_scatter(a, clamp_lanes(nlanes, groups_[gid]), stream));
 }
 
 void Comm::all_reduce(int gid, AllReduceArgs a, int nlanes, cudaStream_t stream) {
   if (a.algo == kMultimem && mc_heap_ == 0) throw Error("multimem all-reduce requested but no multicast mapping exists");
-  begin_call(gid, &a.g, stream);
+  begin_call(gid, &a.g, stream, in_staging(a.buf_off));
   PCCL_CUDA(launch_all_reduce(a, clamp_lanes(nlanes, groups_[gid]), stream));
 }
 
 void Comm::broadcast(int gid, BroadcastArgs a, int nlanes, cudaStream_t stream) {
   if (a.use_multimem && mc_heap_ == 0) throw Error("multimem broadcast requested but no multicast mapping exists");
   if (a.root < 0 || a.root >= group_size(gid)) throw Error("broadcast root outside the group");
-  begin_call(gid, &a.g, stream);
+  begin_call(gid, &a.g, stream, in_staging(a.buf_off));
   PCCL_CUDA(launch_broadcast(a, clamp_lanes(nlanes, groups_[gid]), stream));
 }
 

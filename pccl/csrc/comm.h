@@ -122,16 +122,22 @@ class Comm {
   std::vector<TraceEvent> read_trace(uint64_t* dropped);
 
   // Fill `g` for a launch on `stream` (also used by fused kernels living in other files).
-  void begin_call(int gid, GroupDev* g, cudaStream_t stream);
+  // `uses_staging`: the launch reads or writes the communicator's staging area.  Every group
+  // shares that area, so such launches are ordered with one another across groups and streams.
+  void begin_call(int gid, GroupDev* g, cudaStream_t stream, bool uses_staging = false);
   uint64_t kernels_launched() const { return launches_; }
 
  private:
   int clamp_lanes(int nlanes, const GroupState& gs) const;
+  bool in_staging(uint64_t off) const { return staging_bytes_ > 0 && off >= staging_off_ && off < staging_off_ + staging_bytes_; }
 
   int world_, rank_, nlocal_, device_;
   std::vector<uint64_t> heaps_, sigs_;
   uint64_t mc_heap_, heap_bytes_, sig_bytes_;
   uint64_t staging_off_ = 0, staging_bytes_ = 0;
+  cudaEvent_t staging_tail_ = nullptr;        // last launch that touched the staging area, on any group
+  cudaStream_t staging_stream_ = nullptr;
+  bool staging_used_ = false;
   OffsetAllocator allocator_;
   std::vector<GroupState> groups_;
   Status* status_ = nullptr;      // pinned, mapped: nlocal entries

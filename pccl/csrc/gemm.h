@@ -2,6 +2,12 @@
 //
 //   C[M,N] = A[M,K] * W[N,K]^T (+ bias[N])      bf16 in, fp32 accumulation in TMEM, bf16 out
 //
+// The CTA-pair form also takes either operand "transposed in memory" (a_mn / b_mn below), which
+// gives the three products of a linear layer without a transposing copy:
+//   forward        y  = x  * W^T      A = x  [M,K],            W = W  [N,K]
+//   data gradient  dx = dy * W        A = dy [M,K],            W = W  stored [K,N]  (b_mn)
+//   weight grad.   dW = dy^T * x      A = dy stored [K,M] (a_mn), W = x stored [K,N]  (b_mn)
+//
 // Plain mode: W is one [N,K] matrix in local memory.
 // Fused mode: W is sharded by rows over the P members of a group (member p owns rows
 // [p*N/P, (p+1)*N/P) in its symmetric heap).  The same kernel gathers the shards into a
@@ -32,11 +38,19 @@ struct GemmArgs {
   int* error;           // device int, set non-zero when a bounded wait ran out
   int two_cta;          // use the 2-SM MMA form (cta_group::2, one 256x256 tile per CTA pair); fused mode
                         // then needs an even gather_ctas (gatherers are whole pairs)
+  // ---- operand layouts (CTA-pair form only; both 0 is the plain A[M,K], W[N,K] case)
+  int a_mn;             // A is stored [K, M] row-major (M contiguous); M % 64 == 0
+  int b_mn;             // W is stored [K, N] row-major (N contiguous); N % 64 == 0
   // ---- fused all-gather (gather_ctas == 0: plain GEMM)
   int gather_ctas;      // CTAs that move shards instead of multiplying
   GroupDev g;           // group, epoch, flags (filled by Comm::begin_call)
   uint64_t shard_off;   // offset of the [N/P, K] shard inside every member's heap
   uint32_t* panel_flags;  // device, ceil(N/256) counters, zeroed before the launch
+  // A panel may be read once its counter has reached flag_target.  With gatherer CTAs that is
+  // their number (each adds one per panel).  With gather_ctas == 0 and panel_flags set, somebody
+  // else fills the local buffer and raises the counters (the copy engines, followed by
+  // stream-ordered 32-bit writes of 1): then flag_target is 1 and all CTAs multiply.
+  uint32_t flag_target;
 };
 
 // Launches on `stream`.  Returns cudaErrorInvalidValue for shapes the kernel does not take.

@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(kOptThreads)
 // (softmax - onehot) * grad_scale.  loss_sum accumulates the per-row losses.
 __global__ void __launch_bounds__(512) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
                                                          float* loss_sum, int vocab, int64_t row_stride, float grad_scale,
-                                                         int64_t ignore_index) {
+                                                         int64_t ignore_index, int* bad_targets) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* row_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __shared__ float red[32];
@@ -149,7 +149,12 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_kernel(__nv_bfloat16* __restri
   float sum = 0.f;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += __expf(__bfloat162float(row_s[i]) - mx);
   sum = block_reduce<false>(sum, red);
-  const bool ignored = tgt == ignore_index;
+  // A target outside [0, vocab) that is not the ignore index would index past the row in shared
+  // memory: such a row counts as ignored (no loss, zero gradient) and is reported through
+  // *bad_targets, so a corrupt label never becomes an out-of-bounds access.
+  const bool out_of_range = tgt != ignore_index && (tgt < 0 || tgt >= (int64_t)vocab);
+  if (out_of_range && threadIdx.x == 0 && bad_targets != nullptr) atomicAdd(bad_targets, 1);
+  const bool ignored = tgt == ignore_index || out_of_range;
   if (threadIdx.x == 0 && !ignored) {
     const float lt = __bfloat162float(row_s[tgt]);
     atomicAdd(loss_sum, (mx + logf(sum) - lt));
@@ -205,18 +210,23 @@ cudaError_t launch_adamw(float* master, float* m, float* v, const void* grad, in
 }
 
 cudaError_t launch_ce_fwd_bwd(void* logits_bf16, const int64_t* targets, float* loss_sum, int64_t rows, int vocab,
-                              int64_t row_stride, float grad_scale, int64_t ignore_index, cudaStream_t s) {
+                              int64_t row_stride, float grad_scale, int64_t ignore_index, int* bad_targets,
+                              cudaStream_t s) {
   if (rows == 0) return cudaSuccess;
   const size_t smem = (size_t)vocab * sizeof(__nv_bfloat16);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;   // the row must fit into shared memory
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(ce_fwd_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  // the shared-memory limit is a per-device attribute of the function
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    e = cudaFuncSetAttribute(ce_fwd_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   ce_fwd_bwd_kernel<<<(unsigned)rows, 512, smem, s>>>((__nv_bfloat16*)logits_bf16, targets, loss_sum, vocab, row_stride,
-                                                      grad_scale, ignore_index);
+                                                      grad_scale, ignore_index, bad_targets);
   return cudaGetLastError();
 }
 

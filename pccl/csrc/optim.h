@@ -19,8 +19,11 @@ cudaError_t launch_adamw(float* master, float* m, float* v, const void* grad, in
                          uint64_t n, const AdamWArgs& a, const float* total_sq_norm, cudaStream_t s);
 
 // In place: logits (bf16, rows x vocab) become d(loss)/d(logits) * grad_scale; *loss_sum += sum of row losses.
+// A target that is neither ignore_index nor inside [0, vocab) makes its row count as ignored and
+// adds one to *bad_targets (device int, may be nullptr); nothing is read out of bounds.
 cudaError_t launch_ce_fwd_bwd(void* logits_bf16, const int64_t* targets, float* loss_sum, int64_t rows, int vocab,
-                              int64_t row_stride, float grad_scale, int64_t ignore_index, cudaStream_t s);
+                              int64_t row_stride, float grad_scale, int64_t ignore_index, int* bad_targets,
+                              cudaStream_t s);
 
 // out[c] = sum over rows of X[T, N] (bf16, N % 8 == 0).  partial: R*N floats, counters: ceil(N/64)
 // ints that are zero on entry and zero again on exit.

@@ -63,7 +63,7 @@ void adamw(at::Tensor& master, at::Tensor& m, at::Tensor& v, const at::Tensor& g
 }
 
 void ce_fwd_bwd(at::Tensor& logits, const at::Tensor& targets, at::Tensor& loss_sum, double grad_scale,
-                int64_t ignore_index) {
+                int64_t ignore_index, std::optional<at::Tensor> bad_targets) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kBFloat16,
               "logits must be a 2-D bfloat16 CUDA tensor");
   TORCH_CHECK(logits.stride(1) == 1 && logits.stride(0) % 8 == 0, "logits rows must be contiguous and 16-byte aligned");
@@ -71,9 +71,15 @@ void ce_fwd_bwd(at::Tensor& logits, const at::Tensor& targets, at::Tensor& loss_
   check_flat(targets, "targets", at::kLong);
   check_flat(loss_sum, "loss_sum", at::kFloat);
   TORCH_CHECK(targets.numel() == logits.size(0), "one target per row");
+  int* bad = nullptr;
+  if (bad_targets.has_value()) {
+    check_flat(*bad_targets, "bad_targets", at::kInt);
+    TORCH_CHECK(bad_targets->numel() >= 1, "bad_targets must hold one int32");
+    bad = bad_targets->data_ptr<int>();
+  }
   c10::cuda::CUDAGuard guard(logits.device());
   PCCL_CUDA(launch_ce_fwd_bwd(logits.data_ptr(), targets.data_ptr<int64_t>(), loss_sum.data_ptr<float>(), logits.size(0),
-                              (int)logits.size(1), logits.stride(0), (float)grad_scale, ignore_index,
+                              (int)logits.size(1), logits.stride(0), (float)grad_scale, ignore_index, bad,
                               at::cuda::getCurrentCUDAStream().stream()));
 }
 
@@ -252,5 +258,5 @@ void bind_optim(py::module_& m) {
         py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"),
         py::arg("grad_scale") = 1.0, py::arg("max_grad_norm") = 0.0, py::arg("total_sq_norm") = py::none());
   m.def("ce_fwd_bwd", &ce_fwd_bwd, py::arg("logits"), py::arg("targets"), py::arg("loss_sum"), py::arg("grad_scale"),
-        py::arg("ignore_index") = -100);
+        py::arg("ignore_index") = -100, py::arg("bad_targets") = py::none());
 }

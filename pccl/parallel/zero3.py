@@ -169,6 +169,8 @@ class Zero3Engine:
         self.exp_avg_sq = torch.zeros(total_shard, dtype=torch.float32, device=self.device)
         self.sq_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.loss_sum = torch.zeros(1, dtype=torch.float32, device=self.device)
+        # rows whose target was neither the ignore index nor a valid class (the loss kernel skips them)
+        self.bad_targets = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._init_params(seed)
         # views of every unit in each rotating buffer
         if self.local_only:
@@ -359,11 +361,16 @@ class Zero3Engine:
             gpt.gemm_errors.clear()
             if any(codes):
                 raise RuntimeError(f"a GEMM kernel gave up in a bounded wait (codes {sorted(set(c for c in codes if c))})")
+        bad = int(self.bad_targets.item())
+        if bad:
+            self.bad_targets.zero_()
+            raise ValueError(f"{bad} target ids were outside [0, {self.cfg.vocab}) and not the ignore index; "
+                             "their rows were left out of the loss")
         if self.comm is not None:
             self.comm.check(sync=False)
 
     def _ce(self, logits, targets, loss_sum, grad_scale) -> None:
-        self.C.ce_fwd_bwd(logits, targets, loss_sum, grad_scale, -100)
+        self.C.ce_fwd_bwd(logits, targets, loss_sum, grad_scale, -100, self.bad_targets)
 
     def _native_launches(self) -> int:
         if self.comm is not None and self.comm.native is not None:

@@ -1,8 +1,9 @@
 """Pick the algorithm variant and the number of lanes for one collective call.
 
 ``algorithm="auto"`` consults a table keyed by collective, group size and message size
-that is produced from measured bus bandwidth (``benchmark_raw_collectives`` writes it with
-``--write-tuning-table``).  The reference has no such choice: its caller passes
+that is produced from measured bus bandwidth (``benchmark_raw_collectives/sweep.py`` and the
+two per-collective drivers write it with ``--write-tuning-table``).  The reference has no such
+choice: its caller passes
 ``use_rd`` / ``use_rh`` by hand (``pccl/all_gather.py:98-105``) and its README only says
 that the recursive variants are "typically faster at scale".
 

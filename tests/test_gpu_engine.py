@@ -83,6 +83,32 @@ def test_cross_entropy_forward_backward():
     torch.testing.assert_close(small.float(), r2.grad, rtol=2e-2, atol=1e-6)
 
 
+def test_cross_entropy_reports_targets_outside_the_vocabulary():
+    """A label that is neither a class nor the ignore index must not be used as an index: its row
+    is left out (zero loss, zero gradient) and counted in the error word."""
+    import pccl
+
+    C = pccl._C
+    rows, vocab = 6, 1024
+    g = torch.Generator(device=DEV).manual_seed(3)
+    logits = torch.randn(rows, vocab, device=DEV, generator=g).to(torch.bfloat16)
+    targets = torch.randint(0, vocab, (rows,), device=DEV, generator=g)
+    targets[1] = -1
+    targets[4] = vocab
+    good = torch.tensor([0, 2, 3, 5], device=DEV)
+    ref_in = logits.float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(ref_in[good], targets[good], reduction="sum")
+    ref.backward()
+    loss = torch.zeros(1, device=DEV)
+    bad = torch.zeros(1, dtype=torch.int32, device=DEV)
+    work = logits.clone()
+    C.ce_fwd_bwd(work, targets, loss, 1.0, -100, bad)
+    assert int(bad.item()) == 2
+    torch.testing.assert_close(loss[0], ref.detach(), rtol=1e-4, atol=1e-3)
+    assert torch.all(work[1] == 0) and torch.all(work[4] == 0)
+    torch.testing.assert_close(work.float()[good], ref_in.grad[good], rtol=2e-2, atol=1e-6)
+
+
 def _autograd_reference(cfg, engine, tokens, targets):
     """The same model through torch autograd in fp32 from the engine's master weights."""
     import torch.nn.functional as F
