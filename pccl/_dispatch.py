@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import os
-from typing import Callable, Optional
+from typing import Callable, Optional, Sequence
 
 import torch
 
@@ -15,7 +15,7 @@ def algo_from_flags(algorithm: Optional[str], recursive_flag: bool) -> str:
     """The reference selects with booleans (``use_rd`` / ``use_rh``: recursive, else ring);
     ``algorithm`` is this library's wider choice and wins when given."""
     if algorithm is not None:
-        if algorithm != sch.AUTO and algorithm not in sch.ALGO_IDS:
+        if algorithm not in (sch.AUTO, sch.COPY_ENGINE) and algorithm not in sch.ALGO_IDS:
             raise ValueError(f"unknown algorithm {algorithm!r}")
         return algorithm
     return sch.RECURSIVE if recursive_flag else sch.RING
@@ -28,9 +28,12 @@ NVTX = os.environ.get("PCCL_NVTX", "0") == "1"
 
 
 def run_native(group: Group, async_op: bool, launch: Callable[[], None],
-               label: Optional[Callable[[], str]] = None) -> Optional[Request]:
+               label: Optional[Callable[[], str]] = None, copy_stream: bool = False,
+               tensors: Sequence[torch.Tensor] = ()) -> Optional[Request]:
     """Enqueue ``launch()`` on the current stream, or, for ``async_op``, on the
-    communicator's side stream after everything the current stream has queued so far."""
+    communicator's side stream after everything the current stream has queued so far.
+    ``copy_stream``: an asynchronous call goes to the communicator's second side stream, the one
+    for copy-engine transfers, so that it is not queued behind collective kernels."""
     comm = group.comm
     if NVTX and label is not None:
         inner, name = launch, label()
@@ -45,8 +48,11 @@ def run_native(group: Group, async_op: bool, launch: Callable[[], None],
         launch()
         return None
     cur = torch.cuda.current_stream(comm.device)
-    side = comm.side_stream()
+    side = comm.copy_stream() if copy_stream else comm.side_stream()
     side.wait_stream(cur)
+    for t in tensors:
+        if t.is_cuda and not comm.is_symmetric(t):      # heap tensors are not the caching allocator's
+            t.record_stream(side)
     with torch.cuda.stream(side):
         launch()
         ev = torch.cuda.Event()

@@ -61,6 +61,21 @@ def _all_gather(output_tensor: torch.Tensor, input_tensor: torch.Tensor,
         raise TypeError(
             f"Unsupported group type: {type(group)}. Expected torch.distributed.ProcessGroup or pccl.Group.")
     algo = algo_from_flags(algorithm, use_rd)
+    if algo == sch.COPY_ENGINE:
+        comm = group.comm
+        if not (use_pccl_cpp_backend and _native_ok(group, output_tensor, input_tensor) and not comm.emulated
+                and comm.is_symmetric(input_tensor) and output_tensor.is_contiguous() and input_tensor.is_contiguous()):
+            raise ValueError("algorithm='copy_engine' needs the native backend, one rank per process and an input "
+                             "allocated with pccl.empty_symmetric")
+        native = comm.native
+        nbytes = input_tensor.numel() * input_tensor.element_size()
+
+        def launch_ce():
+            native.all_gather_copy_engine(group.gid, output_tensor, input_tensor)
+
+        return run_native(group, async_op, launch_ce,
+                          lambda: f"pccl.all_gather copy_engine {nbytes}B/rank P={group.size}", copy_stream=True,
+                          tensors=(output_tensor, input_tensor))
     if use_pccl_cpp_backend and _native_ok(group, output_tensor, input_tensor):
         comm = group.comm
         nbytes = input_tensor.numel() * input_tensor.element_size()
@@ -76,7 +91,8 @@ def _all_gather(output_tensor: torch.Tensor, input_tensor: torch.Tensor,
             native.all_gather(group.gid, [output_tensor], [input_tensor], sch.ALGO_IDS[algo], nl)
 
         return run_native(group, async_op, launch,
-                          lambda: f"pccl.all_gather {algo} {nbytes}B/rank P={group.size} lanes={nl}")
+                          lambda: f"pccl.all_gather {algo} {nbytes}B/rank P={group.size} lanes={nl}",
+                          tensors=(output_tensor, input_tensor))
     if algo == sch.AUTO:
         algo = sch.RECURSIVE if sch.is_pow2(group.size) else sch.RING
     p2p.all_gather(output_tensor, input_tensor, group.transport(), algo)

@@ -2,8 +2,11 @@
 
 Signature of ``_all_reduce`` follows ``pccl/all_reduce.py:21-55`` of the reference.  There
 the library path (``use_yacl``) is reduce-scatter into a temporary followed by all-gather
-back (``pccl/src/yacl.cpp:146-177``), in an extension that is never built; here it is one
-two-shot kernel working in place (or, with NVLS, ``multimem.ld_reduce`` + ``multimem.st``).
+back (``pccl/src/yacl.cpp:146-177``), in an extension that is never built.  Here
+``algorithm="ring"`` / ``"recursive"`` (or the reference's flags: ``use_yacl`` with
+``use_rh_and_rd`` for recursive halving + doubling, without it for ring) run that same
+composition as ONE kernel launch, in place; ``"direct"`` / ``"auto"`` is the two-shot kernel
+over the switch (or, with NVLS, ``multimem.ld_reduce`` + ``multimem.st``).
 The reference's silent no-op when neither flag is set (:39-49) is not reproduced.
 """
 from __future__ import annotations
@@ -41,17 +44,23 @@ def _all_reduce(input_tensor: torch.Tensor, group: Optional[Union[dist.ProcessGr
     if native_wanted and _native_ok(group, input_tensor) and input_tensor.is_contiguous():
         comm = group.comm
         nbytes = input_tensor.numel() * input_tensor.element_size()
+        requested = algorithm
+        if requested is None and use_yacl:
+            # the reference's flags: recursive halving + doubling, else ring (pccl/all_reduce.py:39-42)
+            requested = sch.RECURSIVE if (use_rh_and_rd and sch.is_pow2(group.size)) else sch.RING
         algo, nl = tuner.choose("all_reduce", group.size, nbytes // max(1, group.size),
-                                requested=algorithm or sch.AUTO, symmetric_in=comm.is_symmetric(input_tensor),
+                                requested=requested or sch.AUTO, symmetric_in=comm.is_symmetric(input_tensor),
                                 has_multimem=comm.nvls, lanes=lanes, max_lanes=comm.native.max_lanes)
-        algo_id = sch.ALGO_IDS[sch.MULTIMEM if algo == sch.MULTIMEM else sch.DIRECT]
+        if algo in (sch.RING, sch.RECURSIVE) and input_tensor.numel() % group.size != 0:
+            algo = sch.DIRECT        # the two-phase schedules cut the tensor into equal blocks
+        algo_id = sch.ALGO_IDS[algo if algo in (sch.MULTIMEM, sch.RING, sch.RECURSIVE) else sch.DIRECT]
         native = comm.native
 
         def launch():
             native.all_reduce(group.gid, [input_tensor], algo_id, nl, scale)
 
         return run_native(group, async_op, launch,
-                          lambda: f"pccl.all_reduce {algo} {nbytes}B P={group.size} lanes={nl}")
+                          lambda: f"pccl.all_reduce {algo} {nbytes}B P={group.size} lanes={nl}", tensors=(input_tensor,))
     algo = algorithm if algorithm in (sch.RING, sch.RECURSIVE, sch.DIRECT) else None
     if algo is None:
         algo = sch.RECURSIVE if (use_rh_and_rd and sch.is_pow2(group.size)) else sch.RING
@@ -83,7 +92,8 @@ def broadcast(tensor: torch.Tensor, src: int, group=None, async_op: bool = False
         def launch():
             native.broadcast(group.gid, [tensor], src, nl, comm.nvls)
 
-        return run_native(group, async_op, launch, lambda: f"pccl.broadcast root={src} {nbytes}B P={group.size} lanes={nl}")
+        return run_native(group, async_op, launch, lambda: f"pccl.broadcast root={src} {nbytes}B P={group.size} lanes={nl}",
+                          tensors=(tensor,))
     p2p.broadcast(tensor, src, group.transport())
     return completed_request() if async_op else None
 

@@ -30,7 +30,10 @@ def _exchange(send: Optional[torch.Tensor], dst_global: int, recv: Optional[torc
     if not ops:
         return
     # gloo/NCCL report an expired wait as RuntimeError, and a peer whose process has already gone
-    # as RuntimeError too ("connection closed by peer"), sometimes while the operation is being posted
+    # as RuntimeError too ("connection closed by peer"), sometimes while the operation is being
+    # posted.  Only those become PcclTimeoutError: a shape or dtype mismatch, an invalid rank or a
+    # tensor on the wrong device is a programming error and must not look like a lost peer to code
+    # that recovers from lost peers.
     try:
         works = dist.batch_isend_irecv(ops)
         for w in works:
@@ -39,9 +42,24 @@ def _exchange(send: Optional[torch.Tensor], dst_global: int, recv: Optional[torc
             else:
                 w.wait(datetime.timedelta(seconds=timeout_s))
     except RuntimeError as exc:
-        raise PcclTimeoutError(
-            f"p2p step with dst={dst_global} src={src_global} did not complete: {exc}"
-        ) from exc
+        if _looks_like_lost_peer(exc):
+            raise PcclTimeoutError(
+                f"p2p step with dst={dst_global} src={src_global} did not complete: {exc}"
+            ) from exc
+        raise
+
+
+_LOST_PEER_MARKS = ("timed out", "timeout", "time out", "connection closed", "connection reset", "connection refused",
+                    "broken pipe", "socket closed", "peer closed", "remote process exited", "heartbeat",
+                    "application timeout", "watchdog")
+
+
+def _looks_like_lost_peer(exc: BaseException) -> bool:
+    """The messages gloo and NCCL use for an expired wait or a peer whose process is gone."""
+    if isinstance(exc, getattr(dist, "DistBackendError", ())) and "invalid" not in str(exc).lower():
+        return True
+    text = str(exc).lower()
+    return any(mark in text for mark in _LOST_PEER_MARKS)
 
 
 class P2PTransport:
@@ -150,8 +168,11 @@ def broadcast(t: torch.Tensor, src: int, tr: P2PTransport) -> None:
 def barrier(tr: P2PTransport) -> None:
     """Dissemination barrier: ceil(log2 P) rounds of one-word messages."""
     P, r = tr.size, tr.rank
-    token = torch.zeros(1, dtype=torch.int32)
-    got = torch.zeros(1, dtype=torch.int32)
+    # the tokens live where the group's backend can send them from: the device for NCCL, the host for gloo
+    on_gpu = dist.is_initialized() and dist.get_backend(tr.pg) == "nccl" and torch.cuda.is_available()
+    dev = torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
+    token = torch.zeros(1, dtype=torch.int32, device=dev)
+    got = torch.zeros(1, dtype=torch.int32, device=dev)
     d = 1
     while d < P:
         tr.sendrecv(token, (r + d) % P, got, (r - d) % P)

@@ -491,6 +491,13 @@ class Communicator:
             self._side_stream = torch.cuda.Stream(device=self.device, priority=-1)
         return self._side_stream
 
+    def copy_stream(self):
+        """Second side stream: asynchronous copy-engine transfers go here, so they are not queued
+        behind the collective kernels of ``side_stream``."""
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        return self._copy_stream
+
     def close(self) -> None:
         if self._closed:
             return

@@ -157,6 +157,40 @@ void all_gather(Comm& c, int gid, std::vector<at::Tensor> outs, std::vector<at::
   }
 }
 
+// All-gather by the GPU's copy engines: this rank copies every peer's contribution out of the
+// peer's symmetric heap into its own output, one cudaMemcpyAsync per peer on the current stream,
+// peers in ring order (me+1, me+2, ...) so that at any moment every source serves one reader.
+// No kernel runs and no SM is occupied, which is what a gather that overlaps GEMMs wants.
+// There is no handshake with the peers either: the caller guarantees that the peers' inputs are
+// complete before the call and stay unchanged until every rank's copy has finished (parameter
+// shards between two optimizer steps, behind a barrier).  One rank per process only.
+void all_gather_copy_engine(Comm& c, int gid, at::Tensor out, at::Tensor in) {
+  TORCH_CHECK(c.nlocal() == 1, "the copy-engine all-gather runs one rank per process");
+  const GroupState& gs = c.group(gid);
+  TORCH_CHECK(gs.my_index >= 0, "this rank is not a member of the group");
+  const int P = (int)gs.ranks.size(), me = gs.my_index;
+  const int dev = c.device();
+  c10::cuda::CUDAGuard guard(dev);
+  check_tensor(out, "output_tensor", dev);
+  check_tensor(in, "input_tensor", dev);
+  TORCH_CHECK(out.scalar_type() == in.scalar_type(), "input and output dtypes differ");
+  TORCH_CHECK(out.numel() == in.numel() * P, "output_tensor must hold world_size * input elements");
+  const uint64_t n = (uint64_t)in.nbytes();
+  if (n == 0) return;
+  const int64_t in_off = c.offset_of((uint64_t)in.data_ptr(), n, c.rank());
+  TORCH_CHECK(in_off >= 0 || P == 1, "the copy-engine all-gather reads the peers' inputs: allocate input_tensor with "
+                                     "pccl.empty_symmetric");
+  cudaStream_t stream = current_stream(dev);
+  char* o = (char*)out.data_ptr();
+  for (int k = 1; k < P; ++k) {
+    const int p = (me + k) % P;
+    PCCL_CUDA(cudaMemcpyAsync(o + (uint64_t)p * n, (const void*)(c.heap_base(gs.ranks[p]) + (uint64_t)in_off), n,
+                              cudaMemcpyDeviceToDevice, stream));
+  }
+  if (o + (uint64_t)me * n != (char*)in.data_ptr())
+    PCCL_CUDA(cudaMemcpyAsync(o + (uint64_t)me * n, in.data_ptr(), n, cudaMemcpyDeviceToDevice, stream));
+}
+
 // Layout-general all-gather used by the 2-D hierarchy: every quantity is given in bytes.
 void all_gather_raw(Comm& c, int gid, int algo, int nlanes, std::vector<uint64_t> in_ptrs, std::vector<uint64_t> out_ptrs,
                     uint64_t recv_off, uint64_t out_src_stride, uint64_t out_sub_stride, uint64_t src_stride,
@@ -310,6 +344,61 @@ void all_reduce(Comm& c, int gid, std::vector<at::Tensor> ts, int algo, int nlan
   if (n == 0) return;
   cudaStream_t stream = current_stream(dev);
   const int64_t off = symmetric_offset(c, gid, l, ts);
+  const int P = c.group_size(gid);
+  if ((algo == kRing || algo == kRecursive) && P > 1 && n % (uint64_t)P == 0) {
+    // The reference's composition (pccl/src/yacl.cpp:146-177): reduce-scatter, then all-gather, both
+    // ring or both recursive; here one launch per chunk, in place (each rank's block of the sum
+    // is formed in its own slot of the tensor and gathered from there).
+    const uint64_t blk = n / (uint64_t)P;            // elements per rank
+    uint64_t cap = blk;
+    if (off < 0) {
+      // private tensors: partial sums and gathered blocks both pass through the staging area
+      cap = std::min(c.staging_bytes() / (uint64_t)(P - 1) / s, c.staging_bytes() / (uint64_t)P / s) / 8 * 8;
+      TORCH_CHECK(cap > 0, "staging area too small for an all-reduce");
+    } else {
+      cap = c.staging_bytes() / (uint64_t)(P - 1) / s / 8 * 8;   // the reduce-scatter phase stages partial sums
+      TORCH_CHECK(cap > 0, "staging area too small for an all-reduce");
+    }
+    for (uint64_t e0 = 0; e0 < blk; e0 += cap) {
+      const uint64_t len = std::min(cap, blk - e0);
+      AllReduceRsAgArgs a;
+      std::memset(&a, 0, sizeof(a));
+      a.rs.algo = a.ag.algo = algo;
+      a.rs.in_dtype = a.rs.wire_dtype = a.rs.out_dtype = dt;
+      a.rs.nsub = 1;
+      a.rs.scale = (float)scale;
+      a.rs.dst_stride = blk * s;                     // block d of the input starts at d * blk
+      a.rs.out_sub_stride = blk * s;
+      a.rs.stage_off = c.staging_off();
+      a.rs.sub_elems = len;
+      a.ag.nsub = 1;
+      a.ag.sub_bytes = len * s;
+      a.ag.in_sub_stride = blk * s;
+      a.ag.out_src_stride = blk * s;
+      for (int i = 0; i < l.n; ++i) {
+        char* base = (char*)ts[i].data_ptr();
+        const int me = l.first + i;
+        a.rs.in[i] = base + e0 * s;
+        a.rs.out[i] = base + ((uint64_t)me * blk + e0) * s;    // this rank's block of the sum, in its own slot
+        if (off >= 0) {
+          a.ag.in[i] = nullptr;                                  // already in place in the landing zone
+          a.ag.out[i] = nullptr;
+        } else {
+          a.ag.in[i] = base + ((uint64_t)me * blk + e0) * s;
+          a.ag.out[i] = base + e0 * s;
+        }
+      }
+      if (off >= 0) {
+        a.ag.recv_off = (uint64_t)off + e0 * s;      // peers write straight into the symmetric tensor
+        a.ag.src_stride = blk * s;
+      } else {
+        a.ag.recv_off = c.staging_off();
+        a.ag.src_stride = cap * s;
+      }
+      c.all_reduce_rsag(gid, a, nlanes, stream);
+    }
+    return;
+  }
   AllReduceArgs a;
   std::memset(&a, 0, sizeof(a));
   a.algo = algo == kMultimem ? kMultimem : kDirect;
@@ -369,6 +458,81 @@ void broadcast(Comm& c, int gid, std::vector<at::Tensor> ts, int root, int nlane
     for (int i = 0; i < l.n; ++i) b.data[i] = (char*)ts[i].data_ptr() + e0;
     c.broadcast(gid, b, nlanes, stream);
   }
+}
+
+// ------------------------------------------------------------------ entry points under the reference's names
+// pccl.all_gather_mpi / reduce_scatter_mpi(output, input, comm, algorithm) of the reference
+// (pccl/src/pccl.cpp:11-14,87-90) and all_reduce_mpi(tensor, comm, algorithm) of its unbuilt
+// pccl/src/yacl.cpp:146-149.  `comm` is a pccl.Group where the reference takes an mpi4py
+// communicator; `algorithm` is "recursive" (halving / doubling) or "ring".  The argument
+// checks are the reference's (contiguous, 1-D, sizes, dtypes); unlike it, the reductions also
+// take bf16 and fp16, the all-gather has a real ring, and sizes are 64-bit.
+struct GroupRef {
+  std::shared_ptr<Comm> comm;
+  int gid;
+};
+
+GroupRef group_from_python(const py::object& g) {
+  TORCH_CHECK(py::hasattr(g, "comm") && py::hasattr(g, "gid"),
+              "expected a pccl.Group as the communicator argument (it stands where the reference takes an mpi4py communicator)");
+  py::object comm = g.attr("comm");
+  TORCH_CHECK(!comm.is_none() && !comm.attr("native").is_none(), "the group has no native communicator (no CUDA device?)");
+  GroupRef r{comm.attr("native").cast<std::shared_ptr<Comm>>(), g.attr("gid").cast<int>()};
+  TORCH_CHECK(r.comm->nlocal() == 1, "the *_mpi entry points take one tensor per process");
+  return r;
+}
+
+int algo_from_name(const std::string& algorithm, const char* fn) {
+  if (algorithm == "recursive") return kRecursive;
+  if (algorithm == "ring") return kRing;
+  TORCH_CHECK(false, "Unknown algorithm specified for ", fn, ": ", algorithm);
+  return -1;
+}
+
+int default_lanes(const Comm& c, uint64_t bytes) {
+  const uint64_t want = std::max<uint64_t>(1, bytes / (128u << 10));
+  return (int)std::min<uint64_t>(want, (uint64_t)std::min(64, c.max_lanes()));
+}
+
+void check_1d(const at::Tensor& out, const at::Tensor* in) {
+  TORCH_CHECK(out.is_contiguous(), in ? "output tensor must be contiguous." : "input tensor must be contiguous.");
+  if (in) TORCH_CHECK(in->is_contiguous(), "input tensor must be contiguous.");
+  TORCH_CHECK(out.dim() == 1, in ? "output tensor must be 1D" : "input tensor must be 1D");
+  if (in) TORCH_CHECK(in->dim() == 1, "input tensor must be 1D");
+}
+
+void all_gather_mpi(const at::Tensor& output_tensor, const at::Tensor& input_tensor, py::object py_comm,
+                    const std::string& algorithm) {
+  check_1d(output_tensor, &input_tensor);
+  TORCH_CHECK(input_tensor.dtype() == output_tensor.dtype(), "Input and output tensors must have the same dtype.");
+  GroupRef g = group_from_python(py_comm);
+  const int size = g.comm->group_size(g.gid);
+  TORCH_CHECK(output_tensor.numel() == input_tensor.numel() * size,
+              "Output tensor must have total_elem elements (input tensor numel() *world_size)");
+  const int algo = algo_from_name(algorithm, "all_gather_mpi");
+  all_gather(*g.comm, g.gid, {output_tensor}, {input_tensor}, algo, default_lanes(*g.comm, (uint64_t)input_tensor.nbytes()));
+}
+
+void reduce_scatter_mpi(const at::Tensor& output_tensor, const at::Tensor& input_tensor, py::object py_comm,
+                        const std::string& algorithm) {
+  check_1d(output_tensor, &input_tensor);
+  GroupRef g = group_from_python(py_comm);
+  const int size = g.comm->group_size(g.gid);
+  TORCH_CHECK(input_tensor.numel() % size == 0, "Input tensor size must be divisible by number of processes");
+  TORCH_CHECK(output_tensor.numel() == input_tensor.numel() / size,
+              "Output tensor must have block_size elements (input tensor numel()/world_size)");
+  const int algo = algo_from_name(algorithm, "reduce_scatter_mpi");
+  reduce_scatter(*g.comm, g.gid, {output_tensor}, {input_tensor}, algo,
+                 default_lanes(*g.comm, (uint64_t)output_tensor.nbytes()), 1.0, std::nullopt);
+}
+
+void all_reduce_mpi(const at::Tensor& input_tensor, py::object py_comm, const std::string& algorithm) {
+  check_1d(input_tensor, nullptr);
+  GroupRef g = group_from_python(py_comm);
+  const int size = g.comm->group_size(g.gid);
+  TORCH_CHECK(input_tensor.numel() % size == 0, "Input tensor size must be divisible by number of processes");
+  const int algo = algo_from_name(algorithm, "all_reduce_mpi");
+  all_reduce(*g.comm, g.gid, {input_tensor}, algo, default_lanes(*g.comm, (uint64_t)input_tensor.nbytes() / (uint64_t)size), 1.0);
 }
 
 at::Tensor heap_tensor(Comm& c, int64_t off, int64_t numel, at::ScalarType dtype, int world_rank) {
@@ -455,6 +619,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     PCCL_CUDA(cudaMemcpy((void*)addr, &v, 4, cudaMemcpyHostToDevice));
     PCCL_CUDA(cudaDeviceSynchronize());
   });
+  m.def("all_gather_mpi", &all_gather_mpi, py::arg("output_tensor"), py::arg("input_tensor"), py::arg("comm"),
+        py::arg("algorithm") = "recursive", "all-gather on a pccl.Group; algorithm: 'recursive' (doubling) or 'ring'");
+  m.def("reduce_scatter_mpi", &reduce_scatter_mpi, py::arg("output_tensor"), py::arg("input_tensor"), py::arg("comm"),
+        py::arg("algorithm") = "recursive", "reduce-scatter (SUM) on a pccl.Group; algorithm: 'recursive' (halving) or 'ring'");
+  m.def("all_reduce_mpi", &all_reduce_mpi, py::arg("input_tensor"), py::arg("comm"), py::arg("algorithm") = "recursive",
+        "in-place all-reduce (SUM) on a pccl.Group as reduce-scatter + all-gather of one schedule family, one launch");
   m.def("num_steps", [](int algo, int P) { return num_steps(algo, P); });
   m.def("ag_step", [](int algo, int P, int r, int t) { return step_tuple(ag_step(algo, P, r, t)); });
   m.def("rs_step", [](int algo, int P, int r, int t) { return step_tuple(rs_step(algo, P, r, t)); });
@@ -543,6 +713,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("reset_after_failure", &Comm::reset_after_failure)
       .def("all_gather", &all_gather, py::arg("gid"), py::arg("outs"), py::arg("ins"), py::arg("algo"), py::arg("nlanes"))
       .def("all_gather_raw", &all_gather_raw)
+      .def("all_gather_copy_engine", &all_gather_copy_engine, py::arg("gid"), py::arg("out"), py::arg("input"),
+           "peer-to-local copies on the current stream, no kernel; the caller keeps the peers' inputs stable")
       .def("reduce_scatter", &reduce_scatter, py::arg("gid"), py::arg("outs"), py::arg("ins"), py::arg("algo"),
            py::arg("nlanes"), py::arg("scale") = 1.0, py::arg("wire_dtype") = py::none())
       .def("reduce_scatter_raw", &reduce_scatter_raw)

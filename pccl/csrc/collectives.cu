@@ -65,18 +65,18 @@ __device__ __forceinline__ void publish(const GroupDev& g, const LaneCtx& c, int
 }
 
 // ============================================================================ all-gather
-__global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __grid_constant__ AllGatherArgs a) {
-  extern __shared__ __align__(128) unsigned char smem[];
+// The whole all-gather as a device function, so that a kernel can run it after another phase
+// (the two-phase all-reduce below).  `gran`: bytes a lane's range is a multiple of; `coll`: the
+// collective the status word names when a wait gives up.
+__device__ __forceinline__ void all_gather_body(const AllGatherArgs& a, BulkPipe& pipe, uint64_t gran, uint32_t coll) {
   const GroupDev& g = a.g;
   const int P = g.size;
-  const LaneCtx c{(int)blockIdx.y, g.first_local + (int)blockIdx.y, (int)blockIdx.x, kCollAllGather};
+  const LaneCtx c{(int)blockIdx.y, g.first_local + (int)blockIdx.y, (int)blockIdx.x, coll};
   const int me = c.me;
   uint64_t lo, hi;
-  lane_range(a.sub_bytes, 16, c.lane, gridDim.x, &lo, &hi);
+  lane_range(a.sub_bytes, gran, c.lane, gridDim.x, &lo, &hi);
   const uint64_t len = hi - lo;
   if (len == 0) return;  // the same lane is empty on every rank
-  BulkPipe pipe;
-  bulk_pipe_init(pipe, smem, g.timeout_ns);
   const int algo = a.algo;
   char* mine = g.heap[me] + a.recv_off;
   const char* in = a.in[c.li];
@@ -213,6 +213,13 @@ __global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __gri
   cta_bulk_flush();
 }
 
+__global__ void __launch_bounds__(kCollThreads, 1) all_gather_kernel(const __grid_constant__ AllGatherArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  BulkPipe pipe;
+  bulk_pipe_init(pipe, smem, a.g.timeout_ns);
+  all_gather_body(a, pipe, 16, kCollAllGather);
+}
+
 // ============================================================================ reduce-scatter
 // Sum nsrc sources (first one of type TA, the rest TW) into one destination.
 template <int TA, int TW, int TOUT, bool REMOTE_W>
@@ -244,18 +251,15 @@ __device__ __forceinline__ bool lane_reduce(BulkPipe& pipe, char* out, const cha
 }
 
 template <int TIN, int TW, int TOUT>
-__global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const __grid_constant__ ReduceScatterArgs a) {
-  extern __shared__ __align__(128) unsigned char smem[];
+__device__ __forceinline__ void reduce_scatter_body(const ReduceScatterArgs& a, BulkPipe& pipe, uint32_t coll) {
   const GroupDev& g = a.g;
   const int P = g.size;
-  const LaneCtx c{(int)blockIdx.y, g.first_local + (int)blockIdx.y, (int)blockIdx.x, kCollReduceScatter};
+  const LaneCtx c{(int)blockIdx.y, g.first_local + (int)blockIdx.y, (int)blockIdx.x, coll};
   const int me = c.me;
   uint64_t lo, hi;
   lane_range(a.sub_elems, 8, c.lane, gridDim.x, &lo, &hi);
   const uint64_t cnt = hi - lo;
   if (cnt == 0) return;
-  BulkPipe pipe;
-  bulk_pipe_init(pipe, smem, g.timeout_ns);
   const int algo = a.algo;
   const char* in = a.in[c.li] != nullptr ? a.in[c.li] : g.heap[me] + a.in_off;
   char* out = a.out[c.li];
@@ -389,6 +393,34 @@ __global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const _
       }
     if (t < n) publish(g, c, step_kind(algo, t), s.dst);
   }
+}
+
+template <int TIN, int TW, int TOUT>
+__global__ void __launch_bounds__(kCollThreads, 1) reduce_scatter_kernel(const __grid_constant__ ReduceScatterArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  BulkPipe pipe;
+  bulk_pipe_init(pipe, smem, a.g.timeout_ns);
+  reduce_scatter_body<TIN, TW, TOUT>(a, pipe, kCollReduceScatter);
+}
+
+// ============================================================================ all-reduce = reduce-scatter + all-gather
+// The composition the reference's all-reduce uses (pccl/src/yacl.cpp:146-177: reduce-scatter into
+// a temporary, all-gather back; recursive halving + recursive doubling, or ring + ring), as ONE
+// launch: phase one leaves this rank's block of the sum in its slot of the tensor, phase two is
+// the all-gather of those slots with the same schedule family.  The two phases are two calls as
+// far as the flags go (consecutive call numbers), so a step flag of phase one can never be taken
+// for one of phase two; a peer's block is pushed into this rank's tensor only after this rank has
+// signalled its entry into phase two, that is after it has read all of its own input.
+// Lanes keep the same element range in both phases (lane ranges are multiples of 8 elements).
+template <int DT>
+__global__ void __launch_bounds__(kCollThreads, 1) all_reduce_rsag_kernel(const __grid_constant__ AllReduceRsAgArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  BulkPipe pipe;
+  bulk_pipe_init(pipe, smem, a.rs.g.timeout_ns);
+  reduce_scatter_body<DT, DT, DT>(a.rs, pipe, kCollAllReduce);
+  cta_bulk_flush();          // the block written by phase one is what phase two sends
+  __syncthreads();
+  all_gather_body(a.ag, pipe, 8 * Elem<DT>::size, kCollAllReduce);
 }
 
 // ============================================================================ all-reduce
@@ -556,6 +588,26 @@ cudaError_t launch(void (*kernel)(const Args), const Args& args, int nlanes, int
   return cudaGetLastError();
 }
 
+// The two-phase kernel carries two argument blocks; its group geometry is that of the first.
+cudaError_t launch_rsag(void (*kernel)(const AllReduceRsAgArgs), const AllReduceRsAgArgs& args, int nlanes, cudaStream_t stream) {
+  dim3 grid(nlanes, args.rs.g.nlocal), block(kCollThreads);
+  static thread_local const void* configured[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || configured[dev] != reinterpret_cast<const void*>(kernel)) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kBulkSmemBytes);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = reinterpret_cast<const void*>(kernel);
+  }
+  if (args.rs.g.nlocal > 1) {
+    void* params[] = {const_cast<AllReduceRsAgArgs*>(&args)};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, block, params, kBulkSmemBytes, stream);
+  }
+  kernel<<<grid, block, kBulkSmemBytes, stream>>>(args);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 cudaError_t launch_all_gather(const AllGatherArgs& a, int nlanes, cudaStream_t stream) {
@@ -584,6 +636,14 @@ cudaError_t launch_all_reduce(const AllReduceArgs& a, int nlanes, cudaStream_t s
   if (a.dtype == kBF16) return launch(all_reduce_kernel<kBF16>, a, nlanes, kCollThreads, kBulkSmemBytes, stream);
   if (a.dtype == kF16) return launch(all_reduce_kernel<kF16>, a, nlanes, kCollThreads, kBulkSmemBytes, stream);
   if (a.dtype == kF32) return launch(all_reduce_kernel<kF32>, a, nlanes, kCollThreads, kBulkSmemBytes, stream);
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_all_reduce_rsag(const AllReduceRsAgArgs& a, int nlanes, cudaStream_t stream) {
+  const int dt = a.rs.in_dtype;
+  if (dt == kBF16) return launch_rsag(all_reduce_rsag_kernel<kBF16>, a, nlanes, stream);
+  if (dt == kF16) return launch_rsag(all_reduce_rsag_kernel<kF16>, a, nlanes, stream);
+  if (dt == kF32) return launch_rsag(all_reduce_rsag_kernel<kF32>, a, nlanes, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -289,6 +289,16 @@ void Comm::all_reduce(int gid, AllReduceArgs a, int nlanes, cudaStream_t stream)
   PCCL_CUDA(launch_all_reduce(a, clamp_lanes(nlanes, groups_[gid]), stream));
 }
 
+void Comm::all_reduce_rsag(int gid, AllReduceRsAgArgs a, int nlanes, cudaStream_t stream) {
+  if (a.rs.algo != a.ag.algo || (a.rs.algo != kRing && a.rs.algo != kRecursive))
+    throw Error("the two-phase all-reduce runs the ring or the recursive schedules");
+  if (a.rs.algo == kRecursive && !is_pow2(group_size(gid))) throw Error("recursive halving/doubling needs a power-of-two group");
+  const bool staged = in_staging(a.rs.stage_off) || in_staging(a.ag.recv_off);
+  begin_call(gid, &a.rs.g, stream, staged);     // two call numbers: one per phase
+  begin_call(gid, &a.ag.g, stream, staged);
+  PCCL_CUDA(launch_all_reduce_rsag(a, clamp_lanes(nlanes, groups_[gid]), stream));
+}
+
 void Comm::broadcast(int gid, BroadcastArgs a, int nlanes, cudaStream_t stream) {
   if (a.use_multimem && mc_heap_ == 0) throw Error("multimem broadcast requested but no multicast mapping exists");
   if (a.root < 0 || a.root >= group_size(gid)) throw Error("broadcast root outside the group");

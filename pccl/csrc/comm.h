@@ -109,6 +109,8 @@ class Comm {
   void all_gather(int gid, AllGatherArgs a, int nlanes, cudaStream_t stream);
   void reduce_scatter(int gid, ReduceScatterArgs a, int nlanes, cudaStream_t stream);
   void all_reduce(int gid, AllReduceArgs a, int nlanes, cudaStream_t stream);
+  // reduce-scatter + all-gather of the same schedule family (ring / recursive) in one launch
+  void all_reduce_rsag(int gid, AllReduceRsAgArgs a, int nlanes, cudaStream_t stream);
   void broadcast(int gid, BroadcastArgs a, int nlanes, cudaStream_t stream);
   void barrier(int gid, cudaStream_t stream);
 

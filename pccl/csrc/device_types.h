@@ -147,6 +147,13 @@ struct AllReduceArgs {
   float scale;
 };
 
+// All-reduce as reduce-scatter followed by all-gather in one launch (ring or recursive
+// halving/doubling): the two phases with their own group blocks, i.e. their own call numbers.
+struct AllReduceRsAgArgs {
+  ReduceScatterArgs rs;
+  AllGatherArgs ag;
+};
+
 struct BroadcastArgs {
   GroupDev g;
   int root;

@@ -4,6 +4,8 @@
 #include <pybind11/stl.h>
 #include <torch/extension.h>
 
+#include <cuda.h>
+
 #include <optional>
 
 #include "comm.h"
@@ -26,6 +28,16 @@ int sm_count(int device) {
 void check_bf16_2d(const at::Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.dim() == 2 && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), name,
               " must be a contiguous 2-D bfloat16 CUDA tensor");
+}
+
+// One error word per device for every GEMM launch of this process: it stays 0 until a bounded
+// wait of some launch runs out, and is never cleared by a launch (clear it with gemm_reset_error).
+// Sharing it saves a memset per call; the training step issues hundreds of GEMMs.
+at::Tensor& error_word(int device) {
+  static at::Tensor words[64];
+  at::Tensor& w = words[device & 63];
+  if (!w.defined()) w = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  return w;
 }
 
 void fill_common(GemmArgs& a, const at::Tensor& A, const at::Tensor& C, const std::optional<at::Tensor>& bias, int N, int K,
@@ -56,13 +68,44 @@ std::tuple<at::Tensor, at::Tensor> gemm(const at::Tensor& A, const at::Tensor& W
   at::Tensor C = out.has_value() ? *out : at::empty({A.size(0), N}, A.options());
   check_bf16_2d(C, "out");
   TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == N, "out has the wrong shape");
-  at::Tensor err = at::zeros({1}, A.options().dtype(at::kInt));
+  at::Tensor err = error_word(A.get_device());
   GemmArgs a;
   fill_common(a, A, C, bias, N, K, err);
   a.W = W.data_ptr();
   a.two_cta = two_cta ? 1 : 0;
   PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), at::cuda::getCurrentCUDAStream().stream()));
   return {C, err};
+}
+
+// General layouts on the CTA-pair kernel.  C[M,N] = opA * opB with
+//   a_mn false: A is [M,K]            a_mn true: A is [K,M]  (the product uses A^T)
+//   b_mn false: B is [N,K] (B^T used) b_mn true: B is [K,N]
+// so (false,false) is a linear layer's forward, (false,true) its data gradient dy * W and
+// (true,true) its weight gradient dy^T * x.  bias (length N) is optional.
+at::Tensor gemm_ex(const at::Tensor& A, const at::Tensor& B, bool a_mn, bool b_mn, std::optional<at::Tensor> bias,
+                   std::optional<at::Tensor> out) {
+  check_bf16_2d(A, "A");
+  check_bf16_2d(B, "B");
+  const int M = (int)(a_mn ? A.size(1) : A.size(0)), K = (int)(a_mn ? A.size(0) : A.size(1));
+  const int N = (int)(b_mn ? B.size(1) : B.size(0)), Kb = (int)(b_mn ? B.size(0) : B.size(1));
+  TORCH_CHECK(K == Kb, "contraction lengths differ: ", K, " vs ", Kb);
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0, "K and N must be multiples of 8");
+  TORCH_CHECK(!a_mn || M % 64 == 0, "a transposed A needs M % 64 == 0");
+  TORCH_CHECK(!b_mn || N % 64 == 0, "a transposed B needs N % 64 == 0");
+  c10::cuda::CUDAGuard guard(A.device());
+  at::Tensor C = out.has_value() ? *out : at::empty({M, N}, A.options());
+  check_bf16_2d(C, "out");
+  TORCH_CHECK(C.size(0) == M && C.size(1) == N, "out has the wrong shape");
+  at::Tensor err = error_word(A.get_device());
+  GemmArgs a;
+  fill_common(a, A, C, bias, N, K, err);
+  a.M = M;
+  a.W = B.data_ptr();
+  a.two_cta = 1;
+  a.a_mn = a_mn ? 1 : 0;
+  a.b_mn = b_mn ? 1 : 0;
+  PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), at::cuda::getCurrentCUDAStream().stream()));
+  return C;
 }
 
 // U = A @ W^T + bias and G = gelu(U) from one kernel: the first linear layer of a transformer MLP
@@ -77,7 +120,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> gemm_gelu(const at::Tensor& A, co
   c10::cuda::CUDAGuard guard(A.device());
   at::Tensor U = at::empty({A.size(0), N}, A.options());
   at::Tensor G = at::empty({A.size(0), N}, A.options());
-  at::Tensor err = at::zeros({1}, A.options().dtype(at::kInt));
+  at::Tensor err = error_word(A.get_device());
   GemmArgs a;
   fill_common(a, A, U, bias, N, K, err);
   a.W = W.data_ptr();
@@ -87,11 +130,95 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> gemm_gelu(const at::Tensor& A, co
   return {U, G, err};
 }
 
+// ---------------------------------------------------------------- gather by the copy engines
+// The second way to feed the fused kernel: instead of gatherer CTAs, the GPU's copy engines pull
+// the peers' shards into the local buffer (one cudaMemcpyAsync per run of panels on a copy
+// stream), and a stream-ordered 32-bit write raises each panel's flag when its bytes have
+// landed.  All SMs multiply; a tile whose panel has not arrived waits on the flag exactly as
+// it does for gatherer CTAs.  The copies need no SM, so they make progress while the persistent
+// GEMM kernel occupies every SM (a flag-setting kernel could not: it would wait for the GEMM
+// that waits for its flag).  The peers' shards must not change while they are read: this path
+// has no handshake with the peers' kernels, the caller orders it against the writers (ZeRO-3
+// parameters only change in the optimizer step, behind a barrier).
+struct CopyLane {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ready = nullptr, done = nullptr;
+};
+
+CopyLane& copy_lane(int device) {
+  static CopyLane lanes[64];
+  CopyLane& l = lanes[device & 63];
+  if (l.stream == nullptr) {
+    PCCL_CUDA(cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking));
+    PCCL_CUDA(cudaEventCreateWithFlags(&l.ready, cudaEventDisableTiming));
+    PCCL_CUDA(cudaEventCreateWithFlags(&l.done, cudaEventDisableTiming));
+  }
+  return l;
+}
+
+using WriteValue32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+WriteValue32Fn write_value32() {
+  static WriteValue32Fn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || p == nullptr)
+      throw Error("this driver does not offer cuStreamWriteValue32 (stream memory operations)");
+    fn = reinterpret_cast<WriteValue32Fn>(p);
+  }
+  return fn;
+}
+
+// Enqueue the copies and flag writes of one fused call on the device's copy stream, ordered after
+// everything `compute` has queued so far.  `panels_per_copy` <= 0: one copy per peer shard.
+void enqueue_copy_engine_gather(const GemmArgs& a, char* w_full, int panels_per_copy, cudaStream_t compute, int device) {
+  const int P = a.g.size, me = a.g.first_local;
+  const int tpr = (a.N / P) / kGemmBN;
+  const uint64_t panel_bytes = (uint64_t)kGemmBN * a.K * 2;
+  const int ppc = panels_per_copy > 0 ? std::min(panels_per_copy, tpr) : tpr;
+  CopyLane& l = copy_lane(device);
+  WriteValue32Fn wv = write_value32();
+  PCCL_CUDA(cudaEventRecord(l.ready, compute));
+  PCCL_CUDA(cudaStreamWaitEvent(l.stream, l.ready, 0));
+  for (int k = 1; k < P; ++k) {
+    const int p = (me + k) % P;
+    for (int j0 = 0; j0 < tpr; j0 += ppc) {
+      const int n = std::min(ppc, tpr - j0);
+      const uint64_t dst_off = ((uint64_t)p * tpr + j0) * panel_bytes;
+      PCCL_CUDA(cudaMemcpyAsync(w_full + dst_off, a.g.heap[p] + a.shard_off + (uint64_t)j0 * panel_bytes,
+                                (uint64_t)n * panel_bytes, cudaMemcpyDeviceToDevice, l.stream));
+      for (int j = j0; j < j0 + n; ++j) {
+        const CUresult r = wv(reinterpret_cast<CUstream>(l.stream), reinterpret_cast<CUdeviceptr>(a.panel_flags + p * tpr + j), 1u, 0u);
+        if (r != CUDA_SUCCESS) throw Error("cuStreamWriteValue32 failed with code " + std::to_string((int)r));
+      }
+    }
+  }
+  // the own rows last: the kernel multiplies them straight out of the shard, the copy only
+  // completes the gathered weight for whoever uses it afterwards
+  const uint64_t own_bytes = (uint64_t)tpr * panel_bytes;
+  PCCL_CUDA(cudaMemcpyAsync(w_full + (uint64_t)me * own_bytes, a.g.heap[me] + a.shard_off, own_bytes, cudaMemcpyDeviceToDevice,
+                            l.stream));
+}
+
+void finish_copy_engine_gather(cudaStream_t compute, int device) {
+  CopyLane& l = copy_lane(device);
+  PCCL_CUDA(cudaEventRecord(l.done, l.stream));
+  PCCL_CUDA(cudaStreamWaitEvent(compute, l.done, 0));   // later work on `compute` sees the whole gathered weight
+}
+
+int even_gatherers(int gather_ctas, bool two_cta) {
+  return std::max(two_cta ? 2 : 1, two_cta ? (gather_ctas + 1) / 2 * 2 : gather_ctas);
+}
+
 // Fused all-gather + GEMM on a communicator group.  w_shard: this rank's [N/P, K] rows, in
 // the symmetric heap; w_full: local [N, K] buffer that receives the gathered weight.
+// copy_engine: gather with the copy engines (see above) instead of gatherer CTAs.
 std::tuple<at::Tensor, at::Tensor> ag_gemm(Comm& c, int gid, const at::Tensor& A, const at::Tensor& w_shard,
                                            at::Tensor& w_full, std::optional<at::Tensor> bias,
-                                           std::optional<at::Tensor> out, int gather_ctas, bool two_cta) {
+                                           std::optional<at::Tensor> out, int gather_ctas, bool two_cta, bool copy_engine,
+                                           int panels_per_copy) {
   check_bf16_2d(A, "A");
   check_bf16_2d(w_shard, "w_shard");
   check_bf16_2d(w_full, "w_full");
@@ -101,51 +228,62 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm(Comm& c, int gid, const at::Tensor& A
   TORCH_CHECK(A.size(1) == K && w_shard.size(1) == K && w_shard.size(0) * P == N, "shape mismatch between A, shard and full weight");
   TORCH_CHECK(N % (P * kGemmBN) == 0, "every rank must own a multiple of 256 rows");
   TORCH_CHECK(K % 8 == 0, "K must be a multiple of 8");
+  TORCH_CHECK(!copy_engine || two_cta, "the copy-engine gather feeds the CTA-pair kernel only");
   const int64_t off = c.offset_of((uint64_t)w_shard.data_ptr(), (uint64_t)w_shard.nbytes(), c.rank());
   TORCH_CHECK(off >= 0 && off % 16 == 0, "w_shard must live in the symmetric heap (pccl.empty_symmetric)");
   const int dev = c.device();
   c10::cuda::CUDAGuard guard(dev);
   at::Tensor C = out.has_value() ? *out : at::empty({A.size(0), N}, A.options());
   check_bf16_2d(C, "out");
-  at::Tensor err = at::zeros({1}, A.options().dtype(at::kInt));
-  at::Tensor flags = at::zeros({N / kGemmBN}, A.options().dtype(at::kInt));
+  at::Tensor err = error_word(dev);
   GemmArgs a;
   fill_common(a, A, C, bias, N, K, err);
   a.W = w_full.data_ptr();
-  a.gather_ctas = P > 1 ? std::max(two_cta ? 2 : 1, two_cta ? (gather_ctas + 1) / 2 * 2 : gather_ctas) : 0;
   a.two_cta = two_cta ? 1 : 0;
   a.shard_off = (uint64_t)off;
-  a.panel_flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
-  if (P > 1) {
-    c.begin_call(gid, &a.g, stream);
-  } else {
+  if (P == 1) {
     // one rank: the shard is the whole weight; multiply straight out of it
     a.W = w_shard.data_ptr();
     PCCL_CUDA(cudaMemcpyAsync(w_full.data_ptr(), w_shard.data_ptr(), w_shard.nbytes(), cudaMemcpyDeviceToDevice, stream));
+    PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
+    return {C, err};
   }
-  PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
+  at::Tensor flags = at::zeros({N / kGemmBN}, A.options().dtype(at::kInt));
+  a.panel_flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
+  c.begin_call(gid, &a.g, stream);
+  if (copy_engine) {
+    a.gather_ctas = 0;
+    a.flag_target = 1;
+    enqueue_copy_engine_gather(a, (char*)w_full.data_ptr(), panels_per_copy, stream, dev);
+    PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
+    finish_copy_engine_gather(stream, dev);
+  } else {
+    a.gather_ctas = even_gatherers(gather_ctas, two_cta);
+    PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
+  }
   return {C, err};
 }
 
 // Same kernel with peers that are plain local buffers and no handshake: for tests on one GPU.
 std::tuple<at::Tensor, at::Tensor> ag_gemm_local(const at::Tensor& A, std::vector<at::Tensor> shards, int me,
                                                  at::Tensor& w_full, std::optional<at::Tensor> bias, int gather_ctas,
-                                                 bool two_cta) {
+                                                 bool two_cta, bool copy_engine, int panels_per_copy) {
   check_bf16_2d(A, "A");
   check_bf16_2d(w_full, "w_full");
   const int P = (int)shards.size();
   TORCH_CHECK(P >= 2 && P <= kMaxRanks && me >= 0 && me < P, "need 2..8 shards and a valid index");
   const int N = (int)w_full.size(0), K = (int)w_full.size(1);
   TORCH_CHECK(N % (P * kGemmBN) == 0 && K % 8 == 0 && A.size(1) == K, "shape mismatch");
+  TORCH_CHECK(!copy_engine || two_cta, "the copy-engine gather feeds the CTA-pair kernel only");
+  const int dev = A.get_device();
   c10::cuda::CUDAGuard guard(A.device());
   at::Tensor C = at::empty({A.size(0), N}, A.options());
-  at::Tensor err = at::zeros({1}, A.options().dtype(at::kInt));
+  at::Tensor err = error_word(dev);
   at::Tensor flags = at::zeros({N / kGemmBN}, A.options().dtype(at::kInt));
   GemmArgs a;
   fill_common(a, A, C, bias, N, K, err);
   a.W = w_full.data_ptr();
-  a.gather_ctas = std::max(two_cta ? 2 : 1, two_cta ? (gather_ctas + 1) / 2 * 2 : gather_ctas);
   a.two_cta = two_cta ? 1 : 0;
   a.shard_off = 0;
   a.panel_flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
@@ -158,7 +296,17 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm_local(const at::Tensor& A, std::vecto
     TORCH_CHECK(shards[p].size(0) * P == N && shards[p].size(1) == K, "shard has the wrong shape");
     a.g.heap[p] = (char*)shards[p].data_ptr();
   }
-  PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), at::cuda::getCurrentCUDAStream().stream()));
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
+  if (copy_engine) {
+    a.gather_ctas = 0;
+    a.flag_target = 1;
+    enqueue_copy_engine_gather(a, (char*)w_full.data_ptr(), panels_per_copy, stream, dev);
+    PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
+    finish_copy_engine_gather(stream, dev);
+  } else {
+    a.gather_ctas = even_gatherers(gather_ctas, two_cta);
+    PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
+  }
   return {C, err};
 }
 
@@ -168,15 +316,24 @@ void bind_gemm(py::module_& m) {
   m.def("gemm", &gemm, py::arg("A"), py::arg("W"), py::arg("bias") = py::none(), py::arg("out") = py::none(),
         py::arg("two_cta") = true,
         "C = A @ W^T (+bias) on the tcgen05 tensor cores; returns (C, error_flag)");
+  m.def("gemm_ex", &gemm_ex, py::arg("A"), py::arg("B"), py::arg("a_mn") = false, py::arg("b_mn") = false,
+        py::arg("bias") = py::none(), py::arg("out") = py::none(),
+        "C = opA * opB on the CTA-pair tcgen05 kernel; a_mn: A stored [K,M]; b_mn: B stored [K,N] (else [N,K])");
+  m.def("gemm_error_word", [](int device) { return error_word(device); }, py::arg("device"),
+        "the device's shared GEMM error word (0 unless a bounded wait of some launch ran out)");
+  m.def("gemm_reset_error", [](int device) { error_word(device).zero_(); }, py::arg("device"));
   m.def("gemm_gelu", &gemm_gelu, py::arg("A"), py::arg("W"), py::arg("bias") = py::none(), py::arg("two_cta") = true,
         "(U, gelu(U), error_flag) with U = A @ W^T (+bias): activation fused into the GEMM epilogue");
   m.def("ag_gemm_local", &ag_gemm_local, py::arg("A"), py::arg("shards"), py::arg("me"), py::arg("w_full"),
-        py::arg("bias") = py::none(), py::arg("gather_ctas") = 8, py::arg("two_cta") = true);
+        py::arg("bias") = py::none(), py::arg("gather_ctas") = 8, py::arg("two_cta") = true, py::arg("copy_engine") = false,
+        py::arg("panels_per_copy") = 0);
   m.def("ag_gemm",
         [](std::shared_ptr<Comm> c, int gid, const at::Tensor& A, const at::Tensor& w_shard, at::Tensor& w_full,
-           std::optional<at::Tensor> bias, std::optional<at::Tensor> out, int gather_ctas, bool two_cta) {
-          return ag_gemm(*c, gid, A, w_shard, w_full, bias, out, gather_ctas, two_cta);
+           std::optional<at::Tensor> bias, std::optional<at::Tensor> out, int gather_ctas, bool two_cta, bool copy_engine,
+           int panels_per_copy) {
+          return ag_gemm(*c, gid, A, w_shard, w_full, bias, out, gather_ctas, two_cta, copy_engine, panels_per_copy);
         },
         py::arg("comm"), py::arg("gid"), py::arg("A"), py::arg("w_shard"), py::arg("w_full"), py::arg("bias") = py::none(),
-        py::arg("out") = py::none(), py::arg("gather_ctas") = 16, py::arg("two_cta") = true);
+        py::arg("out") = py::none(), py::arg("gather_ctas") = 16, py::arg("two_cta") = true, py::arg("copy_engine") = false,
+        py::arg("panels_per_copy") = 0);
 }

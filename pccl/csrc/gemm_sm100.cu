@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (;;) {
             uint32_t v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            if (v >= (uint32_t)a.gather_ctas) break;
+            if (v >= a.flag_target) break;
             if ((++spins & 63u) == 0u) {
               if (*abort_flag != 0 || global_timer_ns() - t0 > kWaitNs) {
                 ok = false;
@@ -475,18 +475,46 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
 // ---------------------------------------------------------------- 2-SM variant (cta_group::2)
 // A pair of CTAs on neighbouring SMs works on one 256x256 tile.  Each CTA stages its own
-// 128 rows of A and its own 128 rows of W (32 KiB per stage instead of 48, seven stages), the
-// leader CTA issues M=256 MMAs that read both CTAs' shared memory, and each CTA keeps the
-// accumulator rows of its half in its own TMEM.  Per FLOP a third less shared-memory traffic
-// than the single-SM form.  Loads are plain tiled TMA loads (no cluster multicast); both
-// CTAs' loads count on the leader's barrier; commits are sent to each CTA's barrier in turn.
-constexpr int kStages2 = 7;
+// 128 rows of A and its own 128 rows of W (32 KiB per stage, six stages), the leader CTA
+// issues M=256 MMAs that read both CTAs' shared memory, and each CTA keeps the accumulator
+// rows of its half in its own TMEM.  Per FLOP a third less shared-memory traffic than the
+// single-SM form.  Loads are plain tiled TMA loads (no cluster multicast); both CTAs' loads
+// count on the leader's barrier; commits are sent to each CTA's barrier in turn.
+//
+// Operand layouts.  An operand whose contraction index is contiguous in memory (A[M,K],
+// W[N,K]) is loaded as 128 rows x 64 k ("K-major": rows of 128 bytes, 128-byte swizzle).  An
+// operand stored the other way round (A as [K,M], W as [K,N]: what dy^T * x and dy * W read) is
+// loaded as 64 k x 128 rows in two blocks of 64 rows ("MN-major": each k is a row of 128 bytes
+// holding 64 consecutive rows of the operand; blocks 8 KiB apart).  The MMA reads either
+// through its shared-memory descriptor, so no transposing copy exists anywhere.
+//
+// Epilogue.  Every epilogue warp owns 32 accumulator rows.  It reads 64 columns from TMEM,
+// adds the bias, rounds to bf16, writes the 32x64 slab into its own 4 KiB piece of shared
+// memory in the 128-byte-swizzled layout and hands it to the copy engine as one tiled TMA
+// store (which also clips rows and columns beyond M and N); two pieces per warp alternate.
+constexpr int kStages2 = 6;
 constexpr uint32_t kHalfBytes = 128 * BK * 2;              // 16 KiB: 128 rows x 64 bf16
 constexpr uint32_t kStage2Bytes = 2 * kHalfBytes;          // A half + W half
-constexpr uint32_t kBar2Off = kStages2 * kStage2Bytes;     // 229,376
+constexpr uint32_t kEpiOff = kStages2 * kStage2Bytes;      // 196,608
+constexpr uint32_t kEpiSlabBytes = 32 * 64 * 2;            // 4 KiB: 32 rows x 64 bf16
+constexpr uint32_t kEpiWarpBytes = 2 * kEpiSlabBytes;      // two slabs per epilogue warp
+constexpr uint32_t kBar2Off = kEpiOff + 4 * kEpiWarpBytes; // 229,376
 constexpr uint32_t kGemm2Smem = kBar2Off + 256 + 1024;     // 230,656 of the 232,448 a CTA may have
 static_assert(kBulkSmemBytes <= kBar2Off + 256, "the gatherer's copy ring must fit");
 constexpr uint32_t kIdesc2 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+// Descriptor of an MN-major operand tile (64 k x 128 rows as two 8 KiB blocks of 64 rows):
+// leading byte offset = distance between the 64-row blocks, stride byte offset = distance
+// between groups of eight k (8 rows of 128 bytes), 128-byte swizzle, version 1.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(8192 >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -510,12 +538,24 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       "l"(map), "r"(leader_bar), "r"(x), "r"(y)
       : "memory");
 }
-__device__ __forceinline__ void mma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(leader_bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_u32(smem_src)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void mma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc2), "r"(accumulate)
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr) {
@@ -525,9 +565,30 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
+// Round eight accumulator values (+ bias) to bf16; returns them packed, and gelu() of the
+// rounded values in `g` when ACT.
+template <bool ACT>
+__device__ __forceinline__ uint4 pack8(const uint32_t* r, const float* b, uint4* g) {
+  uint32_t w[4], gg[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float x0 = __uint_as_float(r[2 * e]) + b[2 * e], x1 = __uint_as_float(r[2 * e + 1]) + b[2 * e + 1];
+    __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+    w[e] = *reinterpret_cast<uint32_t*>(&h);
+    if (ACT) {
+      __nv_bfloat162 hg = __floats2bfloat162_rn(gelu_tanh(__low2float(h)), gelu_tanh(__high2float(h)));
+      gg[e] = *reinterpret_cast<uint32_t*>(&hg);
+    }
+  }
+  if (ACT) *g = make_uint4(gg[0], gg[1], gg[2], gg[3]);
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     gemm_sm100_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
-                           const __grid_constant__ CUtensorMap tmWown, const __grid_constant__ GemmArgs a) {
+                           const __grid_constant__ CUtensorMap tmWown, const __grid_constant__ CUtensorMap tmC,
+                           const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ GemmArgs a) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   if ((int)blockIdx.x < a.gather_ctas) {      // whole pairs: gather_ctas is even
@@ -571,7 +632,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 
   const int tiles_m = (a.M + 255) / 256, tiles_n = (a.N + 255) / 256;
   const int total = tiles_m * tiles_n;
-  const bool fused = a.gather_ctas > 0;
+  const bool fused = a.panel_flags != nullptr;       // W arrives panel by panel
   const int group_m = fused ? tiles_m : (tiles_m < 8 ? tiles_m : 8);
   const int nkb = (a.K + BK - 1) / BK;
   const int P = a.g.size, me = a.g.first_local;
@@ -608,8 +669,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           uint32_t spins = 0;
           for (;;) {
             uint32_t v;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            if (v >= (uint32_t)a.gather_ctas) break;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v >= a.flag_target) break;
             if ((++spins & 63u) == 0u) {
               if (*abort_flag != 0 || global_timer_ns() - t0 > kWaitNs) {
                 ok = false;
@@ -625,6 +686,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           asm volatile("fence.proxy.async;" ::: "memory");
         }
       }
+      const int ay = m_idx * 256 + (int)rank * 128;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const uint32_t s = it % kStages2, ph = (it / kStages2) & 1u;
         if (!gemm_wait(empty + s, ph ^ 1u, abort_flag)) {
@@ -635,13 +697,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         unsigned char* sa = smem + (size_t)s * kStage2Bytes;
         if (leader) mbar_expect_tx(full + s, 2 * kStage2Bytes);     // both CTAs' bytes land on this barrier
         const uint32_t bar = map_to_cta(smem_u32(full + s), 0);      // the leader's barrier, from either CTA
-        tma_load_2d_pair(sa, &tmA, kb * BK, m_idx * 256 + (int)rank * 128, bar);
-        tma_load_2d_pair(sa + kHalfBytes, wmap, kb * BK, wy, bar);
+        if (A_MN) tma_load_3d_pair(sa, &tmA, 0, kb * BK, ay >> 6, bar);
+        else tma_load_2d_pair(sa, &tmA, kb * BK, ay, bar);
+        if (B_MN) tma_load_3d_pair(sa + kHalfBytes, wmap, 0, kb * BK, wy >> 6, bar);
+        else tma_load_2d_pair(sa + kHalfBytes, wmap, kb * BK, wy, bar);
       }
     }
     if (!ok) *abort_flag = 1;
   } else if (warp == 1 && lane == 0 && leader) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    constexpr uint32_t idesc = kIdesc2 | (A_MN ? (1u << 15) : 0u) | (B_MN ? (1u << 16) : 0u);
+    constexpr uint64_t a_step = A_MN ? (2048 >> 4) : (32 >> 4);   // 16 k further: 16 rows of 128 B, or 32 bytes along the row
+    constexpr uint64_t b_step = B_MN ? (2048 >> 4) : (32 >> 4);
     uint32_t it = 0, tile_count = 0;
     bool ok = true;
     for (int t = pair; t < total && ok; t += npairs, ++tile_count) {
@@ -660,10 +727,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + (size_t)s * kStage2Bytes);
-        const uint64_t da = smem_desc(sa), db = smem_desc(sa + kHalfBytes);
+        const uint64_t da = A_MN ? smem_desc_mn(sa) : smem_desc(sa);
+        const uint64_t db = B_MN ? smem_desc_mn(sa + kHalfBytes) : smem_desc(sa + kHalfBytes);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)
-          mma_bf16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb > 0 || k > 0) ? 1u : 0u);
+          mma_bf16_pair(d_tmem, da + (uint64_t)k * a_step, db + (uint64_t)k * b_step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
         const uint32_t eb = smem_u32(empty + s);
         mma_commit_pair(map_to_cta(eb, 0));     // free the stage in both CTAs
         mma_commit_pair(map_to_cta(eb, 1));
@@ -681,7 +749,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
     uint32_t tile_count = 0;
     bool ok = true;
-    const int lane_base = (warp & 3) * 32;
+    const int q = warp & 3;                     // the quarter of the TMEM lanes this warp may read
+    const int lane_base = q * 32;
+    unsigned char* ebuf = smem + kEpiOff + (size_t)q * kEpiWarpBytes;
+    const bool has_act = a.act_out != nullptr;
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
+    const uint32_t sw = (uint32_t)(lane & 7);   // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)
+    uint32_t nstore = 0;                        // slabs stored so far: picks the piece, across tiles too
     for (int t = pair; t < total && ok; t += npairs, ++tile_count) {
       int m_idx, n_idx;
       decode(t, &m_idx, &n_idx);
@@ -691,20 +765,63 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         break;
       }
       tc_fence_after();
-      const int row = m_idx * 256 + (int)rank * 128 + lane_base + lane;
+      const int row0 = m_idx * 256 + (int)rank * 128 + lane_base;     // first of this warp's 32 rows
       const uint32_t t_base = tmem_base + acc * BN + ((uint32_t)lane_base << 16);
 #pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(t_base + cc * 32, r);
+      for (int slab = 0; slab < BN / 64; ++slab) {
+        uint32_t r[64];
+        tmem_ld32(t_base + slab * 64, r);
+        tmem_ld32(t_base + slab * 64 + 32, r + 32);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int col0 = n_idx * 256 + cc * 32;
-        if (row < a.M && col0 < a.N) epilogue_store32(a, r, row, col0);
+        if (slab == BN / 64 - 1) {
+          // the accumulator is in registers: hand it back to the MMA issuer before storing
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
+        }
+        const int col0 = n_idx * 256 + slab * 64;
+        if (row0 >= a.M || col0 >= a.N) continue;                     // nothing of this slab exists (warp-uniform)
+        unsigned char* cbuf = ebuf + (has_act ? 0u : (nstore & 1u)) * kEpiSlabBytes;
+        unsigned char* gbuf = ebuf + kEpiSlabBytes;
+        ++nstore;
+        // the copy engine must have finished reading the piece that is about to be rewritten:
+        // with two alternating pieces that is the store before the previous one
+        if (lane == 0) {
+          if (has_act) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        }
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (bias != nullptr && col0 + c * 8 < a.N) {
+            const uint4 qv = __ldg(reinterpret_cast<const uint4*>(bias + col0 + c * 8));     // N % 8 == 0: whole and aligned
+            const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              b[2 * e] = __uint_as_float(qw[e] << 16);
+              b[2 * e + 1] = __uint_as_float(qw[e] & 0xffff0000u);
+            }
+          }
+          const uint32_t off = (uint32_t)lane * 128u + (((uint32_t)c ^ sw) << 4);
+          uint4 g;
+          if (has_act) {
+            *reinterpret_cast<uint4*>(cbuf + off) = pack8<true>(r + c * 8, b, &g);
+            *reinterpret_cast<uint4*>(gbuf + off) = g;
+          } else {
+            *reinterpret_cast<uint4*>(cbuf + off) = pack8<false>(r + c * 8, b, &g);
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes, async-proxy read
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmC, cbuf, col0, row0);
+          if (has_act) tma_store_2d(&tmAct, gbuf, col0, row0);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));   // tell the leader's MMA issuer
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has been performed
     if (!ok && lane == 0) {
       atomicCAS(a.error, 0, kErrEpilogue);
       *abort_flag = 1;
@@ -750,41 +867,100 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uin
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Operand stored [K, rows] row-major (rows contiguous, rows % 64 == 0), seen as a 3-D tensor
+// {64 consecutive rows, k, block of 64 rows}: one box of 64 x 64 x 2 lands in shared memory as
+// two 8 KiB blocks, each holding 64 k as rows of 128 bytes (128-byte swizzle).  k beyond K
+// reads zeros; blocks beyond the last one read zeros.
+bool make_map_mn(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr || rows % 64 != 0) return false;
+  cuuint64_t dims[3] = {64, K, rows / 64};
+  cuuint64_t strides[2] = {rows * 2, 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)BK, 2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Output [M, N] bf16 row-major written in boxes of 32 rows x 64 columns (128-byte swizzle).
+bool make_map_store(CUtensorMap* map, void* base, uint64_t M, uint64_t N) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {N, M};
+  cuuint64_t strides[1] = {N * 2};
+  cuuint32_t box[2] = {64, 32};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN>
+cudaError_t launch_pair(const CUtensorMap& mA, const CUtensorMap& mW, const CUtensorMap& mOwn, const CUtensorMap& mC,
+                        const CUtensorMap& mAct, const GemmArgs& a, int grid, cudaStream_t stream) {
+  // the shared-memory limit is an attribute of the function on the current device
+  static thread_local bool configured[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    e = cudaFuncSetAttribute(gemm_sm100_2cta_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemm2Smem);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  gemm_sm100_2cta_kernel<A_MN, B_MN><<<grid, kGemmThreads, kGemm2Smem, stream>>>(mA, mW, mOwn, mC, mAct, a);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
-cudaError_t launch_gemm_sm100(const GemmArgs& a, int sm_count, cudaStream_t stream) {
+cudaError_t launch_gemm_sm100(const GemmArgs& a_in, int sm_count, cudaStream_t stream) {
+  GemmArgs a = a_in;
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K % 8) != 0 || (a.N % 8) != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.C)) & 15u)
     return cudaErrorInvalidValue;
+  if (a.act_out != nullptr && (reinterpret_cast<uintptr_t>(a.act_out) & 15u)) return cudaErrorInvalidValue;
+  const bool fused = a.panel_flags != nullptr;
+  if (a.gather_ctas > 0 && !fused) return cudaErrorInvalidValue;
+  if (fused && a.gather_ctas == 0 && !a.two_cta) return cudaErrorInvalidValue;   // externally filled panels: CTA-pair form only
+  if ((a.a_mn || a.b_mn) && (!a.two_cta || fused)) return cudaErrorInvalidValue;   // layouts: plain CTA-pair form only
+  if (a.a_mn && (a.M % 64) != 0) return cudaErrorInvalidValue;
+  if (a.b_mn && (a.N % 64) != 0) return cudaErrorInvalidValue;
   const void* own = a.W;
   uint64_t own_rows = (uint64_t)a.N;
-  if (a.gather_ctas > 0) {
+  if (fused) {
     const int P = a.g.size;
-    if (P < 1 || a.N % (P * BN) != 0 || a.gather_ctas >= sm_count || a.panel_flags == nullptr) return cudaErrorInvalidValue;
+    if (P < 1 || a.N % (P * BN) != 0 || a.gather_ctas >= sm_count) return cudaErrorInvalidValue;
     own = a.g.heap[a.g.first_local] + a.shard_off;
     own_rows = (uint64_t)a.N / P;
     if (reinterpret_cast<uintptr_t>(own) & 15u) return cudaErrorInvalidValue;
+    if (a.gather_ctas > 0) a.flag_target = (uint32_t)a.gather_ctas;
+    else if (a.flag_target == 0) a.flag_target = 1;
   }
   if (a.two_cta && (a.gather_ctas % 2) == 0) {
-    CUtensorMap mA, mW, mOwn;
-    if (!make_map(&mA, a.A, (uint64_t)a.M, (uint64_t)a.K, 128)) return cudaErrorInvalidValue;
-    if (!make_map(&mW, a.W, (uint64_t)a.N, (uint64_t)a.K, 128)) return cudaErrorInvalidValue;
-    if (!make_map(&mOwn, own, own_rows, (uint64_t)a.K, 128)) return cudaErrorInvalidValue;
-    static thread_local bool configured2[64] = {false};
-    int dev2 = 0;
-    cudaGetDevice(&dev2);
-    if (dev2 < 0 || dev2 >= 64 || !configured2[dev2]) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_sm100_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemm2Smem);
-      if (e != cudaSuccess) return e;
-      if (dev2 >= 0 && dev2 < 64) configured2[dev2] = true;
+    CUtensorMap mA, mW, mOwn, mC, mAct;
+    const bool okA = a.a_mn ? make_map_mn(&mA, a.A, (uint64_t)a.M, (uint64_t)a.K) : make_map(&mA, a.A, (uint64_t)a.M, (uint64_t)a.K, 128);
+    const bool okW = a.b_mn ? make_map_mn(&mW, a.W, (uint64_t)a.N, (uint64_t)a.K) : make_map(&mW, a.W, (uint64_t)a.N, (uint64_t)a.K, 128);
+    if (!okA || !okW) return cudaErrorInvalidValue;
+    if (a.b_mn) mOwn = mW;
+    else if (!make_map(&mOwn, own, own_rows, (uint64_t)a.K, 128)) return cudaErrorInvalidValue;
+    if (!make_map_store(&mC, a.C, (uint64_t)a.M, (uint64_t)a.N)) return cudaErrorInvalidValue;
+    if (a.act_out != nullptr) {
+      if (!make_map_store(&mAct, a.act_out, (uint64_t)a.M, (uint64_t)a.N)) return cudaErrorInvalidValue;
+    } else {
+      mAct = mC;
     }
     const int tiles2 = ((a.M + 255) / 256) * ((a.N + 255) / 256);
     int pairs = (sm_count - a.gather_ctas) / 2;
-    if (a.gather_ctas == 0 && tiles2 < pairs) pairs = tiles2;
+    if (!fused && tiles2 < pairs) pairs = tiles2;
     if (pairs < 1) return cudaErrorInvalidValue;
-    gemm_sm100_2cta_kernel<<<a.gather_ctas + pairs * 2, kGemmThreads, kGemm2Smem, stream>>>(mA, mW, mOwn, a);
-    return cudaGetLastError();
+    const int grid = a.gather_ctas + pairs * 2;
+    if (a.a_mn && a.b_mn) return launch_pair<true, true>(mA, mW, mOwn, mC, mAct, a, grid, stream);
+    if (a.a_mn) return launch_pair<true, false>(mA, mW, mOwn, mC, mAct, a, grid, stream);
+    if (a.b_mn) return launch_pair<false, true>(mA, mW, mOwn, mC, mAct, a, grid, stream);
+    return launch_pair<false, false>(mA, mW, mOwn, mC, mAct, a, grid, stream);
   }
+  if (a.a_mn || a.b_mn) return cudaErrorInvalidValue;
   CUtensorMap tmA, tmW, tmWown;
   if (!make_map(&tmA, a.A, (uint64_t)a.M, (uint64_t)a.K, BM)) return cudaErrorInvalidValue;
   if (!make_map(&tmW, a.W, (uint64_t)a.N, (uint64_t)a.K, BN)) return cudaErrorInvalidValue;
@@ -799,7 +975,7 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a, int sm_count, cudaStream_t stre
   }
   const int tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
   int grid = sm_count;
-  if (a.gather_ctas == 0 && tiles < grid) grid = tiles;
+  if (!fused && tiles < grid) grid = tiles;
   gemm_sm100_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(tmA, tmW, tmWown, a);
   return cudaGetLastError();
 }

@@ -10,6 +10,7 @@ namespace pccl {
 cudaError_t launch_all_gather(const AllGatherArgs& a, int nlanes, cudaStream_t stream);
 cudaError_t launch_reduce_scatter(const ReduceScatterArgs& a, int nlanes, cudaStream_t stream);
 cudaError_t launch_all_reduce(const AllReduceArgs& a, int nlanes, cudaStream_t stream);
+cudaError_t launch_all_reduce_rsag(const AllReduceRsAgArgs& a, int nlanes, cudaStream_t stream);
 cudaError_t launch_broadcast(const BroadcastArgs& a, int nlanes, cudaStream_t stream);
 cudaError_t launch_barrier(const BarrierArgs& a, cudaStream_t stream);
 

@@ -113,3 +113,30 @@ extern "C" int pccl_reduce_scatter_noalloc(const void* const* inputs, void* cons
   if (e != cudaSuccess) return fail(err, err_len, -10, "kernel launch failed (cuda error %lld)", (long long)e);
   return 0;
 }
+
+extern "C" int pccl_reduce_scatter_noalloc_status(cudaStream_t stream, int world, uint32_t* codes, char* err, size_t err_len) {
+  if (codes == nullptr) return fail(err, err_len, -1, "codes must not be null");
+  if (world < 1 || world > PCCL_NOALLOC_MAX_RANKS)
+    return fail(err, err_len, -2, "world size %lld is outside 1..%lld", world, PCCL_NOALLOC_MAX_RANKS);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return fail(err, err_len, -7, "cannot determine the current device (cuda error %lld)", (long long)e);
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    base = g_dev[device].base;
+  }
+  if (base == nullptr) return fail(err, err_len, -11, "no call has been made on device %lld yet", device);
+  e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail(err, err_len, -12, "cudaStreamSynchronize failed (cuda error %lld)", (long long)e);
+  int bad = 0;
+  for (int r = 0; r < world; ++r) {
+    Status s;
+    e = cudaMemcpy(&s, base + (uint64_t)r * kRankStride + kStageStride + kSigStride, sizeof(Status), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(err, err_len, -13, "cudaMemcpy of the status word failed (cuda error %lld)", (long long)e);
+    codes[r] = s.code;
+    if (s.code != kStatusOk) bad = 1;
+  }
+  return bad;
+}

@@ -46,11 +46,22 @@ extern "C" {
 //   dtypes     : 0 = bfloat16, 1 = float16, 2 = float32; out_dtype is in_dtype or float32
 //   algo       : 0 = direct, 1 = ring, 2 = recursive halving (power-of-two world only)
 //   stream     : the stream the work is enqueued on (the call does not wait for it)
-// Returns 0 on success.  On failure returns a negative number and, when `err` is not
-// null, writes a NUL-terminated explanation of at most `err_len` bytes into it.
+// Returns 0 when the arguments were accepted and the work was ENQUEUED on `stream`; that says
+// nothing yet about how the kernel fares.  Every wait inside the kernel is bounded (2 s): a wait
+// that runs out leaves the outputs incomplete and records a status code in the static array,
+// which pccl_reduce_scatter_noalloc_status reads back.  On a rejected argument or a failed
+// enqueue the function returns a negative number and, when `err` is not null, writes a
+// NUL-terminated explanation of at most `err_len` bytes into it.
 int pccl_reduce_scatter_noalloc(const void* const* inputs, void* const* outputs, int world, uint64_t block_elems,
                                 int in_dtype, int out_dtype, int algo, float scale, cudaStream_t stream, char* err,
                                 size_t err_len);
+
+// Outcome of the LAST call on the current device: waits for `stream`, then copies the status
+// code of each of the `world` emulated ranks into codes[0..world) (0 = completed, 1 = a bounded
+// wait ran out, 2 = gave up because another lane had failed).  Allocates nothing.  Returns 0
+// when every rank completed, 1 when some code is non-zero, a negative number on a CUDA error
+// or when no call has been made on this device yet.
+int pccl_reduce_scatter_noalloc_status(cudaStream_t stream, int world, uint32_t* codes, char* err, size_t err_len);
 
 #ifdef __cplusplus
 }

@@ -10,9 +10,14 @@ this module provides them in the form a ZeRO-3 engine wants: parameters grouped 
 backward needs, and a backward that writes weight gradients straight into a flat
 gradient buffer (no autograd graph, no per-parameter ``.grad`` tensors to copy).
 
-GEMMs go to cuBLAS through ``torch``; the two GEMMs that directly consume a freshly
-gathered weight (QKV and FC1) can be replaced by the fused all-gather+GEMM kernel through
-the ``linear_fwd`` hook of ``LayerParams``.  The attention core uses
+Every dense product (the four linear layers of a block forward, their data and weight
+gradients, the output projection and its gradients) runs on this library's tcgen05 GEMM
+(``pccl/csrc/gemm_sm100.cu``) when ``native_gemm`` is on and the operands qualify; the weight and
+data gradients read their operands as they lie in memory (``pccl.ops.gemm.matmul_tn`` /
+``matmul_nn``), so nothing is transposed by a copy.  With ``native_gemm`` off, or for operands the
+kernel does not take, the same products go to cuBLAS through ``torch`` (the baseline arm).  The
+two GEMMs that directly consume a freshly gathered weight (QKV and FC1) can be replaced by the
+fused all-gather+GEMM kernel through the ``linear_fwd`` hook.  The attention core uses
 ``scaled_dot_product_attention`` under a local autograd scope.
 """
 from __future__ import annotations
@@ -142,7 +147,40 @@ LinearFwd = Callable[[torch.Tensor, torch.Tensor, Optional[torch.Tensor], str], 
 
 
 def _default_linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], which: str) -> torch.Tensor:
+    return mm_nt(x, w, b)
+
+
+def _gemm_ok(*ts: torch.Tensor) -> bool:
+    return native_gemm and bool(_kernels()) and all(
+        t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.is_contiguous() and t.data_ptr() % 16 == 0 for t in ts)
+
+
+def mm_nt(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[M,K] @ w[N,K]^T (+ b)."""
+    if _gemm_ok(x, w) and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0 and (b is None or b.is_contiguous()):
+        global native_launches
+        native_launches += 1
+        return _kernels().gemm_ex(x, w, False, False, b, None)
     return F.linear(x, w, b)
+
+
+def mm_nn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a[M,K] @ b[K,N]: the data gradient of a linear layer whose weight is stored [out, in]."""
+    if _gemm_ok(a, b) and (out is None or _gemm_ok(out)) and b.shape[1] % 64 == 0 and b.shape[0] % 8 == 0:
+        global native_launches
+        native_launches += 1
+        return _kernels().gemm_ex(a, b, False, True, None, out)
+    return torch.mm(a, b, out=out) if out is not None else torch.mm(a, b)
+
+
+def mm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a[K,M]^T @ b[K,N]: the weight gradient of a linear layer, operands stored [tokens, features]."""
+    if _gemm_ok(a, b) and (out is None or _gemm_ok(out)) and a.shape[1] % 64 == 0 and b.shape[1] % 64 == 0 \
+            and a.shape[0] % 8 == 0:
+        global native_launches
+        native_launches += 1
+        return _kernels().gemm_ex(a, b, True, True, None, out)
+    return torch.mm(a.t(), b, out=out) if out is not None else torch.mm(a.t(), b)
 
 
 def _ln_fwd(x, w, b, eps, branch=None):
@@ -162,8 +200,8 @@ def _ln_fwd(x, w, b, eps, branch=None):
 
 _native = None
 native_launches = 0     # kernels of this library launched by the functions below
+native_gemm = True       # dense products on the library's tcgen05 GEMM (off: cuBLAS through torch; set by the engine)
 fused_gelu_gemm = False  # FC1 on the tcgen05 GEMM with the GELU in its epilogue (set by the engine)
-gemm_errors: List[torch.Tensor] = []   # error flags of the GEMM launches above, read by the engine's check
 
 
 def _kernels():
@@ -221,8 +259,7 @@ def _fc1_gelu(h: torch.Tensor, p: Dict[str, torch.Tensor], linear_fwd: LinearFwd
     if fused_gelu_gemm and linear_fwd is _default_linear and _fast(h) and _fast(w) and b.is_contiguous() \
             and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
         native_launches += 1
-        u, g, err = _kernels().gemm_gelu(h, w, b)
-        gemm_errors.append(err)
+        u, g, _err = _kernels().gemm_gelu(h, w, b)
         return u, g
     u = linear_fwd(h, w, b, "fc1")
     if _fast(u) and u.numel() % 8 == 0:
@@ -258,10 +295,10 @@ def layer_forward_deferred(x: torch.Tensor, branch: Optional[torch.Tensor], p: D
     with torch.enable_grad():
         att = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True)            # [B, H, S, dh]
     a = att.detach().transpose(1, 2).reshape(T, d)
-    o = torch.addmm(p["proj_b"], a, p["proj_w"].t())
+    o = mm_nt(a, p["proj_w"], p["proj_b"])
     h2, mean2, rstd2, x2 = _ln_fwd(x, p["ln2_w"], p["ln2_b"], cfg.ln_eps, o)       # x2 = x + o, in o's memory
     u, g = _fc1_gelu(h2, p, linear_fwd)                                  # [T, f]
-    m = torch.addmm(p["fc2_b"], g, p["fc2_w"].t())
+    m = mm_nt(g, p["fc2_w"], p["fc2_b"])
     ctx = (x, mean1, rstd1, h1, qd, kd, vd, att, a, x2, mean2, rstd2, h2, u, g)
     return x2, m, ctx
 
@@ -306,30 +343,30 @@ def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[s
 
     def wgrad(dy_, x_, gw):
         if side is None:
-            torch.mm(dy_.t(), x_, out=gw)
+            mm_tn(dy_, x_, out=gw)
             return
         side.wait_stream(main)                  # dy_ and x_ are complete, gw's previous reader is done
         with torch.cuda.stream(side):
-            torch.mm(dy_.t(), x_, out=gw)
+            mm_tn(dy_, x_, out=gw)
 
     if dy_sum is not None:
         gr["fc2_b"].copy_(dy_sum)
     else:
         _bias_grad(dy, gr["fc2_b"])
     wgrad(dy, g, gr["fc2_w"])
-    dg = torch.mm(dy, p["fc2_w"])
+    dg = mm_nn(dy, p["fc2_w"])
     du = _gelu_bwd(dg, u, gr["fc1_b"])
     wgrad(du, h2, gr["fc1_w"])
-    dh2 = torch.mm(du, p["fc1_w"])
+    dh2 = mm_nn(du, p["fc1_w"])
     # dx2 is the gradient of the attention projection's output: its column sums are proj_b's gradient
     dx2 = _ln_bwd(dh2, x2, mean2, rstd2, p["ln2_w"], p["ln2_b"], gr["ln2_w"], gr["ln2_b"], resid=dy, dx_sum=gr["proj_b"])
     wgrad(dx2, a, gr["proj_w"])
-    da = torch.mm(dx2, p["proj_w"])
+    da = mm_nn(dx2, p["proj_w"])
     datt = da.view(batch, S, H, dh).transpose(1, 2)
     dq, dk, dv = torch.autograd.grad(att, (qd, kd, vd), datt)
     dqkv = _cat_qkv_grads(dq, dk, dv, T, d, gr["qkv_b"])
     wgrad(dqkv, h1, gr["qkv_w"])
-    dh1 = torch.mm(dqkv, p["qkv_w"])
+    dh1 = mm_nn(dqkv, p["qkv_w"])
     dx = _ln_bwd(dh1, x, mean1, rstd1, p["ln1_w"], p["ln1_b"], gr["ln1_w"], gr["ln1_b"], resid=dx2, dx_sum=dx_sum)
     if side is not None:
         main.wait_stream(side)                  # the gradient buffer is complete for whoever reads it next
@@ -355,7 +392,7 @@ def embed_backward(dx: torch.Tensor, tokens: torch.Tensor, gr: Dict[str, torch.T
 
 def head_forward_backward(x: torch.Tensor, targets: torch.Tensor, p: Dict[str, torch.Tensor],
                           gr: Dict[str, torch.Tensor], cfg: GPTConfig, grad_scale: float, loss_sum: torch.Tensor,
-                          ce_fwd_bwd: Callable, chunk_tokens: int = 4096,
+                          ce_fwd_bwd: Callable, chunk_tokens: Optional[int] = None,
                           branch: Optional[torch.Tensor] = None, dx_sum: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Final layer norm, tied output projection and cross-entropy, forward and backward in
     one sweep over token chunks so the [T, vocab] logits never exist in full.  Adds the
@@ -363,6 +400,10 @@ def head_forward_backward(x: torch.Tensor, targets: torch.Tensor, p: Dict[str, t
     ``branch`` the input is ``x + branch`` (see ``layer_forward_deferred``); ``dx_sum`` receives the
     column sums of the returned dx (see ``layer_backward``)."""
     T, d = x.shape
+    if chunk_tokens is None:
+        # one chunk while the bf16 logits stay below 2 GiB: then all three products of the head are
+        # single launches of the library GEMM (an accumulating second chunk would need cuBLAS)
+        chunk_tokens = T if T * cfg.vocab * 2 <= (2 << 30) else 4096
     hf, mean, rstd, x = _ln_fwd(x, p["lnf_w"], p["lnf_b"], cfg.ln_eps, branch)
     wte = p["wte"]
     dhf = torch.empty_like(hf)
@@ -371,13 +412,13 @@ def head_forward_backward(x: torch.Tensor, targets: torch.Tensor, p: Dict[str, t
     first = True
     for s in range(0, T, chunk_tokens):
         e = min(T, s + chunk_tokens)
-        logits = torch.mm(hf[s:e], wte.t())                     # [c, V] bf16
+        logits = mm_nt(hf[s:e], wte)                            # [c, V] bf16
         ce_fwd_bwd(logits, tflat[s:e], loss_sum, grad_scale)    # logits -> dlogits, in place
-        torch.mm(logits, wte, out=dhf[s:e])
+        mm_nn(logits, wte, out=dhf[s:e])
         if first:
-            torch.mm(logits.t(), hf[s:e], out=gw)
+            mm_tn(logits, hf[s:e], out=gw)
             first = False
         else:
-            gw.addmm_(logits.t(), hf[s:e])
+            gw.addmm_(logits.t(), hf[s:e])                      # later chunks accumulate: cuBLAS
         del logits
     return _ln_bwd(dhf, x, mean, rstd, p["lnf_w"], p["lnf_b"], gr["lnf_w"], gr["lnf_b"], dx_sum=dx_sum)

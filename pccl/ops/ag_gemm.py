@@ -46,7 +46,8 @@ def auto_gather_ctas(tokens: int, out_features: int, in_features: int, world: in
 
 class AllGatherLinear:
     def __init__(self, comm: Communicator, group: Optional[Group], out_features: int, in_features: int,
-                 gather_ctas: int = 16, device=None, two_cta: bool = True):
+                 gather_ctas: int = 16, device=None, two_cta: bool = True, copy_engine: bool = False,
+                 panels_per_copy: int = 0):
         self.comm = comm
         self.group = group or comm.world_group
         P = self.group.size
@@ -57,6 +58,11 @@ class AllGatherLinear:
         self.N, self.K, self.P = out_features, in_features, P
         self.gather_ctas = gather_ctas       # 0: sized per call from the shapes (auto_gather_ctas)
         self.two_cta = two_cta       # multiply with CTA pairs (cta_group::2, 256x256 tiles)
+        # gather with the GPU's copy engines instead of gatherer CTAs: peer-to-local copies on a
+        # second stream plus one stream-ordered flag write per 256-row panel; every SM multiplies.
+        # No handshake with the peers: their shards must be complete and unchanged during the call.
+        self.copy_engine = copy_engine
+        self.panels_per_copy = panels_per_copy   # 0: one copy per peer shard
         self.w_shard = comm.empty((out_features // P, in_features), torch.bfloat16)
         dev = device or self.w_shard.device
         self.w_full = torch.empty((out_features, in_features), dtype=torch.bfloat16, device=dev)
@@ -65,7 +71,8 @@ class AllGatherLinear:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.K)
         g = self.gather_ctas if self.gather_ctas > 0 else auto_gather_ctas(x2.shape[0], self.N, self.K, self.P)
-        y, err = _C().ag_gemm(self.comm.native, self.group.gid, x2, self.w_shard, self.w_full, bias, None, g, self.two_cta)
+        y, err = _C().ag_gemm(self.comm.native, self.group.gid, x2, self.w_shard, self.w_full, bias, None, g, self.two_cta,
+                              self.copy_engine, self.panels_per_copy)
         if check:
             code = int(err.item())
             self.comm.check(sync=False)

@@ -95,7 +95,8 @@ class Zero3Engine:
     def __init__(self, cfg: GPTConfig, backend: Optional[TorchBackend] = None, optim: Optional[OptimConfig] = None,
                  device: Optional[torch.device] = None, seed: int = 1234, comm=None, group=None,
                  linear_fwd: Optional[Callable] = None, micro_batch: int = 1, fused_ag_gemm: bool = False,
-                 gather_ctas: int = 16, fused_gelu_gemm: bool = False, overlap_wgrad: bool = False):
+                 gather_ctas: int = 16, fused_gelu_gemm: bool = False, overlap_wgrad: bool = False,
+                 native_gemm: bool = True, copy_engine_gather: bool = False):
         from .. import build_kernels
 
         self.C = build_kernels.load()
@@ -108,6 +109,12 @@ class Zero3Engine:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.comm = comm
         self.linear_fwd = linear_fwd or gpt._default_linear
+        # every dense product of the model on the library's tcgen05 GEMM (False: cuBLAS through torch,
+        # which is what the baseline arm measures)
+        self.native_gemm = bool(native_gemm)
+        # parameter gathers by the GPU's copy engines instead of gather kernels (no SM is taken from
+        # the GEMMs they overlap); needs symmetric parameter shards
+        self.copy_engine_gather = bool(copy_engine_gather)
         # FC1 on the library's tcgen05 GEMM with bias and GELU in its epilogue (one kernel, two outputs)
         self.fused_gelu_gemm = bool(fused_gelu_gemm)
         # weight-gradient GEMMs on a second stream, beside the memory-bound kernels of the backward chain
@@ -187,14 +194,21 @@ class Zero3Engine:
             self.gviews0 = gpt.views(self.units[0], self.gradbuf0)
         self.main = torch.cuda.current_stream(self.device)
         self._cur = None
-        self._gemm_errs: List[torch.Tensor] = []
         self._dx_sums = None
         self._fused_gid = None
-        if self.fused_ag_gemm:
+        self._flat_group = None
+        self.copy_engine_gather = self.copy_engine_gather and sym and P > 1
+        if self.fused_ag_gemm or self.copy_engine_gather:
             from ..patch_deepspeed import get_heir_pg
 
-            self._fused_gid = get_heir_pg().get_flat_group().gid
+            self._flat_group = get_heir_pg().get_flat_group()
+            self._fused_gid = self._flat_group.gid
+        if self.fused_ag_gemm:
             self.linear_fwd = self._fused_linear
+        if self.copy_engine_gather:
+            # the copy-engine gathers have no handshake with the peers: every rank's shard must be
+            # complete before anybody reads it
+            dist.barrier(group=group)
         self._rs_pending: List = [None, None]
         self._tokens_dev: Optional[torch.Tensor] = None
         self._targets_dev: Optional[torch.Tensor] = None
@@ -228,6 +242,13 @@ class Zero3Engine:
             if ri in skip:
                 continue
             out = self.gathered[slot][g_off: g_off + g_len]
+            if self.copy_engine_gather:
+                from ..all_gather import all_gather as pccl_all_gather
+                from .. import schedule as sch
+
+                hs.append(pccl_all_gather(out, self._region_shard(self.param_shard, ui, ri), group=self._flat_group,
+                                          async_op=True, algorithm=sch.COPY_ENGINE))
+                continue
             hs.append(self.backend.all_gather_into_tensor(out, self._region_shard(self.param_shard, ui, ri),
                                                           group=self.group, async_op=True))
         return hs[0] if len(hs) == 1 else _Handles(hs)
@@ -257,8 +278,8 @@ class Zero3Engine:
         n_rows, k = w.shape
         shard = self._region_shard(self.param_shard, li, ri).view(n_rows // self.world, k)
         gid = self._fused_gid
-        y, err = self.C.ag_gemm(self.comm.native, gid, x, shard, w, b, None, self.gather_ctas)
-        self._gemm_errs.append(err)
+        y, _err = self.C.ag_gemm(self.comm.native, gid, x, shard, w, b, None, self.gather_ctas, True,
+                                 self.copy_engine_gather, 0)
         return y
 
     # ------------------------------------------------------------------ one training step
@@ -292,6 +313,7 @@ class Zero3Engine:
         x = gpt.embed_forward(tokens, self.pviews[0][0])
         branch = None          # MLP output of the previous block; the next layer norm adds it to x in its own pass
         gpt.fused_gelu_gemm = self.fused_gelu_gemm
+        gpt.native_gemm = self.native_gemm
         saved = []
         for li in range(1, L + 1):
             slot = li % 2
@@ -347,20 +369,24 @@ class Zero3Engine:
         C.adamw(self.master, self.exp_avg, self.exp_avg_sq, self.grad_shard, self.param_shard, o.lr, o.beta1, o.beta2,
                 o.eps, o.weight_decay, self.step_count, 1.0, o.max_grad_norm,
                 self.sq_norm if o.max_grad_norm > 0 else None)
-        own = 2 + (1 if o.max_grad_norm > 0 else 0) + (T + 4095) // 4096
-        self._gemm_errs.clear()
-        del gpt.gemm_errors[:-64]                     # keep the latest flags for check_errors
+        if self.copy_engine_gather:
+            # the next step's copy-engine gathers read the peers' shards without a handshake: nobody
+            # may start them before every rank's optimizer has written its shard (device barrier
+            # kernel on this stream; the host does not wait)
+            from ..all_reduce import barrier as pccl_barrier
+
+            pccl_barrier(self._flat_group, host_sync=False)
+        ce_chunks = 1 if T * cfg.vocab * 2 <= (2 << 30) else (T + 4095) // 4096
+        own = 2 + (1 if o.max_grad_norm > 0 else 0) + ce_chunks  # norm, AdamW, loss kernel per chunk of the head
         self.launches = own + (self._native_launches() + gpt.native_launches - launches0)
         return self.loss_sum / T
 
     def check_errors(self) -> None:
         """Synchronise and raise if a kernel of the last steps gave up in a bounded wait."""
         torch.cuda.synchronize(self.device)
-        if gpt.gemm_errors:
-            codes = torch.stack([e.view(()) for e in gpt.gemm_errors]).tolist()
-            gpt.gemm_errors.clear()
-            if any(codes):
-                raise RuntimeError(f"a GEMM kernel gave up in a bounded wait (codes {sorted(set(c for c in codes if c))})")
+        from ..ops.gemm import check_errors as check_gemm_errors
+
+        check_gemm_errors(self.device)
         bad = int(self.bad_targets.item())
         if bad:
             self.bad_targets.zero_()

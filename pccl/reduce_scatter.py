@@ -86,7 +86,8 @@ def _reduce_scatter(output_tensor: torch.Tensor, input_tensor: torch.Tensor,
             native.reduce_scatter(group.gid, [output_tensor], [input_tensor], sch.ALGO_IDS[algo], nl, scale, wire_dtype)
 
         return run_native(group, async_op, launch,
-                          lambda: f"pccl.reduce_scatter {algo} {nbytes}B/rank P={group.size} lanes={nl}")
+                          lambda: f"pccl.reduce_scatter {algo} {nbytes}B/rank P={group.size} lanes={nl}",
+                          tensors=(output_tensor, input_tensor))
     if algo == sch.AUTO:
         algo = sch.RECURSIVE if sch.is_pow2(group.size) else sch.RING
     p2p.reduce_scatter(output_tensor, input_tensor, group.transport(), algo, scale, wire_dtype)

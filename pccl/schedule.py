@@ -20,6 +20,9 @@ RECURSIVE = "recursive"
 PULL = "pull"
 MULTIMEM = "multimem"
 AUTO = "auto"
+# all-gather only: peer-to-local copies by the GPU's copy engines, no kernel and no handshake; the
+# caller guarantees that the peers' inputs do not change while the call is in flight
+COPY_ENGINE = "copy_engine"
 
 ALGO_IDS = {DIRECT: 0, RING: 1, RECURSIVE: 2, PULL: 3, MULTIMEM: 4}
 ALGO_NAMES = {v: k for k, v in ALGO_IDS.items()}

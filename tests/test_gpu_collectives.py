@@ -339,3 +339,132 @@ def test_python_api_on_single_rank_world():
     req.wait()
     pccl.barrier(g)
     comm.check()
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+@pytest.mark.parametrize("algo", [sch.RING, sch.RECURSIVE])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_all_reduce_as_reduce_scatter_plus_all_gather_in_one_launch(P, algo, dtype):
+    """The reference's composition (recursive halving + doubling, or ring + ring) as one kernel:
+    private tensors (staged) and symmetric tensors (zero-copy), several sizes, back to back."""
+    comm = emu(P)
+    gid = comm.world_group.gid
+    for n in [P, 8 * P, 1000 * P, P * ((1 << 16) + 3)]:
+        ts = [rand(n, dtype, 13 * r + n) for r in range(P)]
+        want = sum(t.float() for t in ts) * 0.5
+        comm.native.all_reduce(gid, ts, sch.ALGO_IDS[algo], 4, 0.5)
+        comm.check()
+        for r in range(P):
+            # bf16 partial sums are rounded once per step of the schedule (up to P-1 times on the ring)
+            tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else \
+                dict(rtol=3e-2, atol=2e-2 * float(want.abs().max()) + 1e-3)
+            torch.testing.assert_close(ts[r].float(), want, **tol)
+            assert torch.equal(ts[r], ts[0]), "all ranks must hold bit-identical results"
+    n = P * 5000
+    sym = comm.empty(n, dtype)
+    vals = [rand(n, dtype, 77 + r) for r in range(P)]
+    for rep in range(2):
+        for r in range(P):
+            sym[r].copy_(vals[r])
+        comm.native.all_reduce(gid, sym, sch.ALGO_IDS[algo], 3, 1.0)
+        comm.check()
+        want = sum(v.float() for v in vals)
+        for r in range(P):
+            tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else \
+                dict(rtol=3e-2, atol=2e-2 * float(want.abs().max()) + 1e-3)
+            torch.testing.assert_close(sym[r].float(), want, **tol)
+    del sym
+    # a count that the group size does not divide falls back to the two-shot kernel in the Python layer
+    if P > 2:
+        g = comm.world_group
+        assert g.size == P
+
+
+BIG = 9 * (1 << 20) + 24          # elements: > 1 MiB per lane on 4-7 lanes, odd tail, 16-byte aligned start
+
+
+@pytest.mark.parametrize("P", [2, 4])
+def test_copy_engine_paths_carry_bf16(P):
+    """Sizes that give every lane more than a megabyte: bf16 data then goes through the copy-engine
+    ring (cp.async.bulk) of every collective, which the small cases above never reach: all-gather
+    direct with several destinations, reduce-scatter pull and the final step of the push variants
+    (bf16 -> bf16 and bf16 -> fp32), all-reduce.  Against fp32 PyTorch sums."""
+    comm = pccl.Communicator.emulated_world(P, device=0, heap_bytes=(P + 2) * BIG * 2 * 2 + (96 << 20), staging_bytes=P * BIG * 2 + (8 << 20))
+    gid = comm.world_group.gid
+    n = BIG
+    # all-gather, symmetric output (zero-copy) and private output
+    sym_out = comm.empty(P * n, torch.bfloat16)
+    vals = [rand(n, torch.bfloat16, 5 + r) for r in range(P)]
+    want = torch.cat(vals)
+    for algo in (sch.DIRECT, sch.RING, sch.PULL):
+        for r in range(P):
+            sym_out[r].zero_()
+        comm.native.all_gather(gid, sym_out, vals, sch.ALGO_IDS[algo], 6)
+        comm.check()
+        for r in range(P):
+            assert torch.equal(sym_out[r], want), f"all_gather {algo} rank {r}"
+    priv = [torch.zeros(P * n, dtype=torch.bfloat16, device=DEV) for _ in range(P)]
+    comm.native.all_gather(gid, priv, vals, sch.ALGO_IDS[sch.DIRECT], 7)
+    comm.check()
+    for r in range(P):
+        assert torch.equal(priv[r], want)
+    del sym_out, priv
+    # reduce-scatter: pull from symmetric inputs, push variants from private inputs
+    m = n // P // 8 * 8
+    sym_in = comm.empty(P * m, torch.bfloat16)
+    ins = [rand(P * m, torch.bfloat16, 40 + r) for r in range(P)]
+    for r in range(P):
+        sym_in[r].copy_(ins[r])
+    for tout in (torch.bfloat16, torch.float32):
+        wantr = rs_reference(ins, P, m, 1.0 / P, tout)
+        outs = [torch.zeros(m, dtype=tout, device=DEV) for _ in range(P)]
+        comm.native.reduce_scatter(gid, outs, sym_in, sch.ALGO_IDS[sch.PULL], 4, 1.0 / P, None)
+        comm.check()
+        for r in range(P):
+            tol = dict(rtol=1e-5, atol=1e-5) if tout == torch.float32 else dict(rtol=8e-3, atol=1e-5)
+            torch.testing.assert_close(outs[r].float(), wantr[r].float(), **tol)
+        for algo in (sch.DIRECT, sch.RING):
+            outs = [torch.zeros(m, dtype=tout, device=DEV) for _ in range(P)]
+            comm.native.reduce_scatter(gid, outs, ins, sch.ALGO_IDS[algo], 4, 1.0 / P, None)
+            comm.check()
+            for r in range(P):
+                tol = dict(rtol=3e-2, atol=3e-2) if algo == sch.RING else \
+                    (dict(rtol=1e-5, atol=1e-5) if tout == torch.float32 else dict(rtol=8e-3, atol=1e-5))
+                torch.testing.assert_close(outs[r].float(), wantr[r].float(), **tol)
+    del sym_in
+    # all-reduce, private tensors, two-shot and two-phase
+    for algo in (sch.DIRECT, sch.RING):
+        ts = [rand(P * m, torch.bfloat16, 90 + r) for r in range(P)]
+        want_ar = sum(t.float() for t in ts)
+        comm.native.all_reduce(gid, ts, sch.ALGO_IDS[algo], 4, 1.0)
+        comm.check()
+        for r in range(P):
+            torch.testing.assert_close(ts[r].float(), want_ar, rtol=3e-2, atol=2e-2 * float(want_ar.abs().max()))
+    comm.close()
+
+
+def test_collectives_of_different_groups_share_the_staging_area_in_order():
+    """Two groups of one communicator use the same staging bytes.  An asynchronous all-gather on
+    group A (side stream, private output: staged) followed at once by a reduce-scatter on group B
+    (current stream, push variant: staged) must not overlap on a rank; both results are checked."""
+    comm = pccl.Communicator.emulated_world(4, device=0, heap_bytes=64 << 20, staging_bytes=16 << 20)
+    ga = comm.world_group
+    gb = comm.new_group([0, 1, 2, 3])
+    n = 300000
+    side = torch.cuda.Stream(device=0)
+    for rep in range(3):
+        ins = [rand(n, torch.float32, rep * 10 + r) for r in range(4)]
+        outs = [torch.zeros(4 * n, device=DEV) for _ in range(4)]
+        big = [rand(4 * n, torch.float32, 50 + rep * 10 + r) for r in range(4)]
+        red = [torch.zeros(n, device=DEV) for _ in range(4)]
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            comm.native.all_gather(ga.gid, outs, ins, sch.ALGO_IDS[sch.RING], 4)
+        comm.native.reduce_scatter(gb.gid, red, big, sch.ALGO_IDS[sch.DIRECT], 4, 1.0, None)
+        torch.cuda.synchronize()
+        comm.check()
+        want = rs_reference(big, 4, n, 1.0, torch.float32)
+        for r in range(4):
+            assert torch.equal(outs[r], torch.cat(ins)), f"all_gather rep {rep} rank {r}"
+            torch.testing.assert_close(red[r], want[r], rtol=1e-5, atol=1e-5)
+    comm.close()

@@ -105,3 +105,70 @@ def test_fused_gather_gemm_with_local_peers(P, me, two_cta):
     W = torch.cat(shards)
     assert torch.equal(w_full, W), "the gathered weight must be a bit-exact copy of the shards"
     check_close(y, A.float() @ W.float().t() + bias.float(), K)
+
+
+@pytest.mark.parametrize("P,me,ppc", [(2, 1, 0), (4, 0, 1), (8, 6, 0)])
+def test_fused_gather_gemm_fed_by_the_copy_engines(P, me, ppc):
+    """The other way to feed the fused kernel: no gatherer CTAs; copies on a second stream bring
+    the panels, stream-ordered 32-bit writes raise their flags, every CTA multiplies."""
+    import pccl
+
+    M, K = 768, 1024
+    N = P * 256 * 2
+    A = rnd((M, K), 12)
+    shards = [rnd((N // P, K), 60 + p, 0.05) for p in range(P)]
+    bias = rnd((N,), 41)
+    w_full = torch.zeros((N, K), device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):                      # twice: the copy stream and its events are reused
+        y, err = pccl._C.ag_gemm_local(A, shards, me, w_full, bias, 0, True, True, ppc)
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0
+        W = torch.cat(shards)
+        assert torch.equal(w_full, W)
+        check_close(y, A.float() @ W.float().t() + bias.float(), K)
+        w_full.zero_()
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 256), (960, 512, 328), (4096, 2048, 8192),
+                                   (8192, 8192, 2048)])
+def test_gemm_data_gradient_layout(shape):
+    """dx = dy @ W with W stored [K_contract, N]: the second operand is read 'transposed in memory'."""
+    import pccl
+
+    M, N, K = shape
+    dy, W = rnd((M, K), 1), rnd((K, N), 2, 0.05)
+    y = pccl._C.gemm_ex(dy, W, False, True)
+    torch.cuda.synchronize()
+    assert int(pccl._C.gemm_error_word(0).item()) == 0
+    check_close(y, dy.float() @ W.float(), K)
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 256), (2048, 2048, 8192), (6144, 2048, 8192), (50304, 1024, 4096),
+                                   (320, 192, 1000)])
+def test_gemm_weight_gradient_layout(shape):
+    """dW = dy^T @ x with both operands stored [tokens, features]: both are read 'transposed in
+    memory', including a token count that is not a multiple of the 64-wide k block and an output
+    that is not a multiple of the 256-wide tile."""
+    import pccl
+
+    M, N, K = shape
+    dy, x = rnd((K, M), 1, 0.1), rnd((K, N), 2, 0.1)
+    out = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+    y = pccl._C.gemm_ex(dy, x, True, True, None, out)
+    torch.cuda.synchronize()
+    assert int(pccl._C.gemm_error_word(0).item()) == 0
+    assert y.data_ptr() == out.data_ptr()
+    check_close(y, dy.float().t() @ x.float(), K)
+
+
+def test_gemm_transposed_first_operand_only():
+    import pccl
+
+    M, N, K = 384, 512, 320
+    a, w = rnd((K, M), 3), rnd((N, K), 4, 0.1)
+    bias = rnd((N,), 5)
+    y = pccl._C.gemm_ex(a, w, True, False, bias)
+    torch.cuda.synchronize()
+    check_close(y, a.float().t() @ w.float().t() + bias.float(), K)
+    with pytest.raises(RuntimeError):
+        pccl._C.gemm_ex(rnd((64, 100), 1), w[:, :64].contiguous(), True, False)     # M = 100 is not a multiple of 64

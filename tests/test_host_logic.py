@@ -313,3 +313,18 @@ def test_committed_tuning_table_is_well_formed():
                 assert algo in sch.ALGO_IDS and algo not in (sch.MULTIMEM,) and nl >= 1
                 if coll == "reduce_scatter":
                     assert algo != sch.PULL         # pull reads the peers' inputs: they must be symmetric
+
+
+def test_only_lost_peers_become_timeouts():
+    """Errors of a p2p step are sorted by what they say: an expired wait or a closed connection is a
+    lost peer (PcclTimeoutError); a mismatch of shapes or dtypes, an invalid rank or a tensor on the
+    wrong device is a programming error and keeps its own type."""
+    from pccl.backends.p2p import _looks_like_lost_peer
+
+    for msg in ("[../third_party/gloo/gloo/transport/tcp/unbound_buffer.cc:81] Timed out waiting 2000ms for recv operation to complete",
+                "Connection closed by peer [127.0.0.1]:5291", "Connection reset by peer", "Broken pipe",
+                "wait timeout after 1000ms"):
+        assert _looks_like_lost_peer(RuntimeError(msg)), msg
+    for msg in ("Tensors must be CUDA and dense", "Invalid destination rank: 7", "size mismatch: expected 8 got 4",
+                "No backend type associated with device type cpu", "Invalid scalar type"):
+        assert not _looks_like_lost_peer(RuntimeError(msg)), msg

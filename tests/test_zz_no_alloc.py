@@ -47,9 +47,24 @@ def _call(fn, ins, outs, world, n, tin, tout, algo, scale):
 _CODE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
+def _status(world):
+    """Status codes of the last call, one per emulated rank, read through the exported query."""
+    from pccl import build_kernels
+
+    lib = ctypes.CDLL(str(build_kernels._SO))
+    q = lib.pccl_reduce_scatter_noalloc_status
+    q.restype = ctypes.c_int
+    q.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_uint32), ctypes.c_char_p, ctypes.c_size_t]
+    codes = (ctypes.c_uint32 * world)()
+    err = ctypes.create_string_buffer(256)
+    rc = q(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), world, codes, err, 256)
+    assert rc in (0, 1), err.value.decode()
+    return list(codes)
+
+
 @pytest.mark.parametrize("world,algo", [(8, 0), (8, 1), (8, 2), (4, 2), (3, 1), (2, 0), (1, 0)])
 @pytest.mark.parametrize("dtypes", [(torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16),
-                                    (torch.float32, torch.float32)])
+                                    (torch.float32, torch.float32), (torch.float16, torch.float16)])
 def test_matches_regular_entry_point_twice(world, algo, dtypes):
     import pccl
 
@@ -66,6 +81,7 @@ def test_matches_regular_entry_point_twice(world, algo, dtypes):
         rc, msg = _call(fn, ins, got, world, n, _CODE[tin], _CODE[tout], algo, 0.5)
         assert rc == 0, msg
         torch.cuda.synchronize()
+        assert _status(world) == [0] * world       # the return code only says "enqueued"; this says "completed"
         ref = (sum(t.float() for t in ins).view(world, n) * 0.5)
         for r in range(world):
             tol = dict(rtol=1e-5, atol=1e-5) if tout == torch.float32 and (tin == torch.float32 or algo == 0) \
