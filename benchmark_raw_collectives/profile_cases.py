@@ -5,6 +5,11 @@
     python benchmark_raw_collectives/profile_cases.py reduce_scatter
     python benchmark_raw_collectives/profile_cases.py adamw
     python benchmark_raw_collectives/profile_cases.py cross_entropy
+    python benchmark_raw_collectives/profile_cases.py gemm_nn | gemm_tn | gemm_split
+    python benchmark_raw_collectives/profile_cases.py all_gather_ring | all_gather_recursive
+    python benchmark_raw_collectives/profile_cases.py reduce_scatter_ring | reduce_scatter_recursive
+    python benchmark_raw_collectives/profile_cases.py all_reduce | all_reduce_ring | broadcast
+    python benchmark_raw_collectives/profile_cases.py layer_norm | gelu | col_sum
 
 Each case launches its kernel three times on inputs larger than the 126 MB L2 but well
 under a few GB, then exits.  Meant to be run plainly first and then under
@@ -85,7 +90,129 @@ def cross_entropy():
     torch.cuda.synchronize()
 
 
+def gemm_nn():
+    """Data gradient dy @ W: 8192 x 2048 out of K = 8192, second operand read as stored [K, N]."""
+    M, N, K = 8192, 2048, 8192
+    dy = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    W = (torch.randn(K, N, device=DEV) * 0.02).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(3):
+        pccl._C.gemm_ex(dy, W, False, True, None, out)
+    torch.cuda.synchronize()
+
+
+def gemm_tn():
+    """Weight gradient dy^T @ x: 8192 x 2048 out of 8192 tokens, both operands read as stored."""
+    M, N, K = 8192, 2048, 8192
+    dy = torch.randn(K, M, device=DEV).to(torch.bfloat16)
+    x = torch.randn(K, N, device=DEV).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(3):
+        pccl._C.gemm_ex(dy, x, True, True, None, out)
+    torch.cuda.synchronize()
+
+
+def gemm_split():
+    """64 tiles on 74 CTA pairs: every tile is split along K and finished from fp32 partial sums."""
+    M, N, K = 2048, 2048, 8192
+    A = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    W = (torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16)
+    flush = torch.empty(256 << 20, device=DEV, dtype=torch.uint8)
+    for _ in range(3):
+        flush.zero_()                                # operands are smaller than L2: start every launch cold
+        pccl._C.gemm_ex(A, W, False, False, None, None)
+    torch.cuda.synchronize()
+
+
+def _ag(algo):
+    comm = _emu()
+    n = 32 << 20
+    outs = comm.empty(8 * n, torch.uint8)
+    ins = [torch.randint(0, 255, (n,), device=DEV, dtype=torch.uint8) for _ in range(8)]
+    for _ in range(3):
+        comm.native.all_gather(comm.world_group.gid, outs, ins, sch.ALGO_IDS[algo], 16)
+    comm.check()
+
+
+def _rs(algo):
+    comm = pccl.Communicator.emulated_world(8, device=0, heap_bytes=640 << 20, staging_bytes=64 << 20)
+    n = 4 << 20
+    ins = [torch.randn(8 * n, device=DEV).to(torch.bfloat16) for _ in range(8)]
+    outs = [torch.empty(n, device=DEV, dtype=torch.float32) for _ in range(8)]
+    for _ in range(3):
+        comm.native.reduce_scatter(comm.world_group.gid, outs, ins, sch.ALGO_IDS[algo], 16, 0.125, None)
+    comm.check()
+
+
+def _ar(algo):
+    comm = pccl.Communicator.emulated_world(8, device=0, heap_bytes=640 << 20, staging_bytes=64 << 20)
+    n = 32 << 20                                    # 64 MiB of bf16 per rank
+    sym = comm.empty(n, torch.bfloat16)
+    for t in sym:
+        t.copy_(torch.randn(n, device=DEV).to(torch.bfloat16))
+    for _ in range(3):
+        comm.native.all_reduce(comm.world_group.gid, sym, sch.ALGO_IDS[algo], 16, 1.0)
+    comm.check()
+
+
+def broadcast():
+    comm = _emu()
+    n = 32 << 20
+    sym = comm.empty(n, torch.uint8)
+    for _ in range(3):
+        comm.native.broadcast(comm.world_group.gid, sym, 0, 16, False)
+    comm.check()
+
+
+def layer_norm():
+    """Residual add + layer norm forward, and the backward with residual, parameter gradients and column sums."""
+    T, d = 32768, 2048                              # 134 MB per bf16 tensor
+    C = pccl._C
+    x = torch.randn(T, d, device=DEV).to(torch.bfloat16)
+    br = torch.randn(T, d, device=DEV).to(torch.bfloat16)
+    w, b = torch.ones(d, device=DEV, dtype=torch.bfloat16), torch.zeros(d, device=DEV, dtype=torch.bfloat16)
+    dy = torch.randn(T, d, device=DEV).to(torch.bfloat16)
+    gw, gb, dsum = torch.empty_like(w), torch.empty_like(b), torch.empty_like(b)
+    for _ in range(3):
+        y, mean, rstd = C.ln_fwd(x, br, w, b, 1e-5)
+        C.ln_bwd(dy, br, mean.view(-1), rstd.view(-1), w, gw, gb, dy, dsum)
+    torch.cuda.synchronize()
+
+
+def gelu():
+    T, f = 8192, 8192
+    C = pccl._C
+    u = torch.randn(T, f, device=DEV).to(torch.bfloat16)
+    dg = torch.randn(T, f, device=DEV).to(torch.bfloat16)
+    gb = torch.empty(f, device=DEV, dtype=torch.bfloat16)
+    for _ in range(3):
+        C.gelu(u)
+        C.gelu_bwd_col_sum(dg, u, gb)
+    torch.cuda.synchronize()
+
+
+def col_sum():
+    T, d = 32768, 2048
+    C = pccl._C
+    x = torch.randn(T, d, device=DEV).to(torch.bfloat16)
+    out = torch.empty(d, device=DEV, dtype=torch.bfloat16)
+    q = torch.randn(T, d, device=DEV).to(torch.bfloat16)
+    gb = torch.empty(3 * d, device=DEV, dtype=torch.bfloat16)
+    for _ in range(3):
+        C.col_sum(x, out)
+        C.cat3_col_sum(q, q, q, gb)
+    torch.cuda.synchronize()
+
+
+CASES = {
+    "gemm": gemm, "gemm_nn": gemm_nn, "gemm_tn": gemm_tn, "gemm_split": gemm_split,
+    "all_gather": all_gather, "all_gather_ring": lambda: _ag(sch.RING), "all_gather_recursive": lambda: _ag(sch.RECURSIVE),
+    "reduce_scatter": reduce_scatter, "reduce_scatter_ring": lambda: _rs(sch.RING),
+    "reduce_scatter_recursive": lambda: _rs(sch.RECURSIVE),
+    "all_reduce": lambda: _ar(sch.DIRECT), "all_reduce_ring": lambda: _ar(sch.RING), "broadcast": broadcast,
+    "adamw": adamw, "cross_entropy": cross_entropy, "layer_norm": layer_norm, "gelu": gelu, "col_sum": col_sum,
+}
+
 if __name__ == "__main__":
-    {"gemm": gemm, "all_gather": all_gather, "reduce_scatter": reduce_scatter, "adamw": adamw,
-     "cross_entropy": cross_entropy}[sys.argv[1]]()
+    CASES[sys.argv[1]]()
     print("done", sys.argv[1])

@@ -51,7 +51,31 @@ struct GemmArgs {
   // else fills the local buffer and raises the counters (the copy engines, followed by
   // stream-ordered 32-bit writes of 1): then flag_target is 1 and all CTAs multiply.
   uint32_t flag_target;
+  // ---- split of the last wave along K (CTA-pair form, plain mode; sk_tiles == 0: off)
+  // With T tiles on G CTA pairs the last of ceil(T/G) rounds is only partly filled.  The first
+  // sk_tiles tiles (in schedule order) are therefore not dealt out whole: their k-blocks form one
+  // sequence that is cut into G equal runs, one per pair, so a tile may be computed by two (or
+  // more) pairs.  The pair that holds a tile's first k-block finishes the tile; every other pair
+  // with a piece of it writes its fp32 partial sums to its slot of sk_scratch and publishes
+  // sk_epoch in sk_flags; the finisher adds them in its epilogue.  A pair works on its run first
+  // and on whole tiles afterwards, so a partial is ready long before its finisher asks for it.
+  int sk_tiles;
+  float* sk_scratch;    // per pair 2 x 128 x 256 floats (256 KiB)
+  uint32_t* sk_flags;   // per pair 8 words (one per epilogue warp of the pair), holding the last epoch written
+  uint32_t sk_epoch;    // differs from launch to launch on the same scratch
+  // ---- tuning knobs (0: the default)
+  int max_pairs;        // use at most this many CTA pairs (plain mode)
+  int group_m;          // row-tiles per band of the tile walk (plain mode; default 8); negative: bands of
+                        // -group_m column-tiles walked along M instead
 };
+
+// Bytes of sk_scratch / words of sk_flags needed for `pairs` CTA pairs.
+constexpr size_t kGemmSkScratchBytesPerPair = 2 * 128 * 256 * sizeof(float);
+constexpr size_t kGemmSkFlagsPerPair = 8;
+
+// How many leading tiles launch_gemm_sm100 would split along K for this shape on `sm_count` SMs
+// (0: none).  The caller provides scratch for sm_count / 2 pairs when this is non-zero.
+int gemm_sk_tiles(int M, int N, int K, int sm_count);
 
 // Launches on `stream`.  Returns cudaErrorInvalidValue for shapes the kernel does not take.
 cudaError_t launch_gemm_sm100(const GemmArgs& a, int sm_count, cudaStream_t stream);

@@ -6,6 +6,8 @@
 
 #include <cuda.h>
 
+#include <map>
+#include <mutex>
 #include <optional>
 
 #include "comm.h"
@@ -38,6 +40,47 @@ at::Tensor& error_word(int device) {
   at::Tensor& w = words[device & 63];
   if (!w.defined()) w = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
   return w;
+}
+
+// Scratch for tiles that are split along K (see GemmArgs::sk_tiles): one buffer per device and
+// stream, allocated on first use and kept, with a launch counter that makes every launch's flags
+// distinct.  Launches that share a stream run one after the other, so they can share the scratch.
+struct SkWorkspace {
+  at::Tensor scratch, flags;
+  uint32_t epoch = 0;
+};
+bool g_split_last_wave = true;
+int g_max_pairs = 0, g_group_m = 0;      // tuning knobs, 0: the kernel's defaults
+
+SkWorkspace& sk_workspace(int device, cudaStream_t stream, int pairs) {
+  static std::map<std::pair<int, cudaStream_t>, SkWorkspace> all;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
+  SkWorkspace& w = all[{device, stream}];
+  const int64_t floats = (int64_t)pairs * (int64_t)(kGemmSkScratchBytesPerPair / sizeof(float));
+  if (!w.scratch.defined() || w.scratch.numel() < floats) {
+    w.scratch = at::empty({floats}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device));
+    w.flags = at::zeros({(int64_t)pairs * (int64_t)kGemmSkFlagsPerPair}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+    w.epoch = 0;
+  }
+  return w;
+}
+
+// Decide whether this plain CTA-pair launch splits its last round along K, and wire the scratch in.
+void maybe_split_last_wave(GemmArgs& a, int device, cudaStream_t stream) {
+  a.max_pairs = g_max_pairs;
+  a.group_m = g_group_m;
+  if (g_max_pairs > 0) return;           // a reduced grid is for measurements of the plain walk
+  if (!g_split_last_wave || !a.two_cta || a.panel_flags != nullptr) return;
+  const int sms = sm_count(device);
+  const int n = gemm_sk_tiles(a.M, a.N, a.K, sms);
+  if (n <= 0) return;
+  SkWorkspace& w = sk_workspace(device, stream, sms / 2);
+  a.sk_tiles = n;
+  a.sk_scratch = w.scratch.data_ptr<float>();
+  a.sk_flags = reinterpret_cast<uint32_t*>(w.flags.data_ptr<int>());
+  a.sk_epoch = ++w.epoch;
+  if (a.sk_epoch == 0) a.sk_epoch = ++w.epoch;      // 0 is what fresh flags hold
 }
 
 void fill_common(GemmArgs& a, const at::Tensor& A, const at::Tensor& C, const std::optional<at::Tensor>& bias, int N, int K,
@@ -73,7 +116,9 @@ std::tuple<at::Tensor, at::Tensor> gemm(const at::Tensor& A, const at::Tensor& W
   fill_common(a, A, C, bias, N, K, err);
   a.W = W.data_ptr();
   a.two_cta = two_cta ? 1 : 0;
-  PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), at::cuda::getCurrentCUDAStream().stream()));
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+  maybe_split_last_wave(a, A.get_device(), stream);
+  PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), stream));
   return {C, err};
 }
 
@@ -104,7 +149,9 @@ at::Tensor gemm_ex(const at::Tensor& A, const at::Tensor& B, bool a_mn, bool b_m
   a.two_cta = 1;
   a.a_mn = a_mn ? 1 : 0;
   a.b_mn = b_mn ? 1 : 0;
-  PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), at::cuda::getCurrentCUDAStream().stream()));
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+  maybe_split_last_wave(a, A.get_device(), stream);
+  PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), stream));
   return C;
 }
 
@@ -126,7 +173,9 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> gemm_gelu(const at::Tensor& A, co
   a.W = W.data_ptr();
   a.act_out = G.data_ptr();
   a.two_cta = two_cta ? 1 : 0;
-  PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), at::cuda::getCurrentCUDAStream().stream()));
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
+  maybe_split_last_wave(a, A.get_device(), stream);
+  PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), stream));
   return {U, G, err};
 }
 
@@ -319,6 +368,13 @@ void bind_gemm(py::module_& m) {
   m.def("gemm_ex", &gemm_ex, py::arg("A"), py::arg("B"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("bias") = py::none(), py::arg("out") = py::none(),
         "C = opA * opB on the CTA-pair tcgen05 kernel; a_mn: A stored [K,M]; b_mn: B stored [K,N] (else [N,K])");
+  m.def("gemm_set_split_last_wave", [](bool on) { g_split_last_wave = on; }, py::arg("on"),
+        "split the tiles of a partly filled last round along K over all CTA pairs (default on)");
+  m.def("gemm_set_tuning", [](int max_pairs, int group_m) { g_max_pairs = max_pairs; g_group_m = group_m; },
+        py::arg("max_pairs") = 0, py::arg("group_m") = 0,
+        "measurement knobs of the CTA-pair kernel: cap on the CTA pairs used, row-tiles per band of the tile walk (0: defaults)");
+  m.def("gemm_sk_tiles", &gemm_sk_tiles, py::arg("M"), py::arg("N"), py::arg("K"), py::arg("sm_count"),
+        "how many leading tiles a plain launch of this shape splits along K (0: none)");
   m.def("gemm_error_word", [](int device) { return error_word(device); }, py::arg("device"),
         "the device's shared GEMM error word (0 unless a bounded wait of some launch ran out)");
   m.def("gemm_reset_error", [](int device) { error_word(device).zero_(); }, py::arg("device"));

@@ -584,6 +584,43 @@ __device__ __forceinline__ uint4 pack8(const uint32_t* r, const float* b, uint4*
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// The work of one CTA pair as a sequence of items (tile, first k-block, end k-block): first its
+// run of the k-block sequence of the leading sk_tiles tiles (see GemmArgs), then whole tiles
+// sk_tiles + pair, + npairs, ...  Producer, MMA issuer and epilogue walk the same sequence.
+struct WorkIter {
+  long long cur, end;     // position in the k-block sequence of the split tiles
+  int nkb, next_tile, total, stride;
+  __device__ __forceinline__ WorkIter(int pair, int npairs, int total_, int nkb_, int sk_tiles)
+      : nkb(nkb_), next_tile(sk_tiles + pair), total(total_), stride(npairs) {
+    const long long I = (long long)sk_tiles * nkb_;
+    cur = I * pair / npairs;
+    end = I * (pair + 1) / npairs;
+  }
+  __device__ __forceinline__ bool next(int* tile, int* kb0, int* kb1) {
+    if (cur < end) {
+      const int t = (int)(cur / nkb);
+      const int k0 = (int)(cur - (long long)t * nkb);
+      const long long left = end - cur;
+      const int k1 = (long long)(nkb - k0) <= left ? nkb : (int)(k0 + left);
+      *tile = t;
+      *kb0 = k0;
+      *kb1 = k1;
+      cur += k1 - k0;
+      return true;
+    }
+    if (next_tile < total) {
+      *tile = next_tile;
+      *kb0 = 0;
+      *kb1 = nkb;
+      next_tile += stride;
+      return true;
+    }
+    return false;
+  }
+};
+// The pair whose run of the split sequence (I k-blocks over G pairs) holds k-block i.
+__device__ __forceinline__ int sk_pair_of(long long i, long long I, int G) { return (int)(((i + 1) * G + I - 1) / I) - 1; }
+
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     gemm_sm100_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
@@ -633,18 +670,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   const int tiles_m = (a.M + 255) / 256, tiles_n = (a.N + 255) / 256;
   const int total = tiles_m * tiles_n;
   const bool fused = a.panel_flags != nullptr;       // W arrives panel by panel
-  const int group_m = fused ? tiles_m : (tiles_m < 8 ? tiles_m : 8);
+  // Tiles are walked in bands: `group` row-tiles deep and all column-tiles wide (or, transposed,
+  // `group` column-tiles wide and all row-tiles deep), down the short side of the band first.
+  const bool walk_n = !fused && a.group_m < 0;            // bands of column-tiles
+  const int want = a.group_m > 0 ? a.group_m : (a.group_m < 0 ? -a.group_m : 8);
+  const int major = walk_n ? tiles_n : tiles_m, minor = walk_n ? tiles_m : tiles_n;
+  const int group = fused ? tiles_m : (major < want ? major : want);
   const int nkb = (a.K + BK - 1) / BK;
   const int P = a.g.size, me = a.g.first_local;
   const int tpr = fused ? (a.N / P) / BN : 0;            // 256-row panels per rank
   auto decode = [&](int t, int* m_idx, int* n_idx) {
-    const int band_tiles = group_m * tiles_n;
+    const int band_tiles = group * minor;
     const int band = t / band_tiles;
-    const int first_m = band * group_m;
-    const int rows = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
+    const int first = band * group;
+    const int depth = (major - first) < group ? (major - first) : group;
     const int in_band = t - band * band_tiles;
-    const int q = in_band / rows;
-    *m_idx = first_m + in_band - q * rows;
+    const int q = in_band / depth;
+    const int along = first + in_band - q * depth;
+    if (walk_n) {
+      *n_idx = along;
+      *m_idx = q;
+      return;
+    }
+    *m_idx = along;
     // fused: own panels first, then the peers' in the order in which they arrive
     *n_idx = fused ? ((me + q / tpr) % P) * tpr + q % tpr : q;
   };
@@ -653,7 +701,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     // ------------------------------------------------------------ TMA producer (both CTAs)
     uint32_t it = 0;
     bool ok = true;
-    for (int t = pair; t < total && ok; t += npairs) {
+    WorkIter work(pair, npairs, total, nkb, a.sk_tiles);
+    int t, kb0, kb1;
+    while (ok && work.next(&t, &kb0, &kb1)) {
       int m_idx, n_idx;
       decode(t, &m_idx, &n_idx);
       const CUtensorMap* wmap = &tmW;
@@ -687,7 +737,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         }
       }
       const int ay = m_idx * 256 + (int)rank * 128;
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const uint32_t s = it % kStages2, ph = (it / kStages2) & 1u;
         if (!gemm_wait(empty + s, ph ^ 1u, abort_flag)) {
           ok = false;
@@ -711,7 +761,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     constexpr uint64_t b_step = B_MN ? (2048 >> 4) : (32 >> 4);
     uint32_t it = 0, tile_count = 0;
     bool ok = true;
-    for (int t = pair; t < total && ok; t += npairs, ++tile_count) {
+    WorkIter work(pair, npairs, total, nkb, a.sk_tiles);
+    int t, kb0, kb1;
+    for (; ok && work.next(&t, &kb0, &kb1); ++tile_count) {
       const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
       if (!gemm_wait(tmem_empty + acc, acc_ph ^ 1u, abort_flag)) {
         ok = false;
@@ -719,7 +771,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
-      for (int kb = 0; kb < nkb; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const uint32_t s = it % kStages2, ph = (it / kStages2) & 1u;
         if (!gemm_wait(full + s, ph, abort_flag)) {
           ok = false;
@@ -731,7 +783,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         const uint64_t db = B_MN ? smem_desc_mn(sa + kHalfBytes) : smem_desc(sa + kHalfBytes);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)
-          mma_bf16_pair(d_tmem, da + (uint64_t)k * a_step, db + (uint64_t)k * b_step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          mma_bf16_pair(d_tmem, da + (uint64_t)k * a_step, db + (uint64_t)k * b_step, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
         const uint32_t eb = smem_u32(empty + s);
         mma_commit_pair(map_to_cta(eb, 0));     // free the stage in both CTAs
         mma_commit_pair(map_to_cta(eb, 1));
@@ -756,7 +808,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
     const uint32_t sw = (uint32_t)(lane & 7);   // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)
     uint32_t nstore = 0;                        // slabs stored so far: picks the piece, across tiles too
-    for (int t = pair; t < total && ok; t += npairs, ++tile_count) {
+    WorkIter work(pair, npairs, total, nkb, a.sk_tiles);
+    const long long sk_I = (long long)a.sk_tiles * nkb;
+    // this warp's 32 x 256 fp32 block inside a pair's scratch slot, and its flag word
+    const size_t sk_warp = ((size_t)rank * 4 + (size_t)q) * (32 * 256);
+    const uint32_t sk_word = rank * 4 + (uint32_t)q;
+    int t, kb0, kb1;
+    for (; ok && work.next(&t, &kb0, &kb1); ++tile_count) {
       int m_idx, n_idx;
       decode(t, &m_idx, &n_idx);
       const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
@@ -767,6 +825,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       tc_fence_after();
       const int row0 = m_idx * 256 + (int)rank * 128 + lane_base;     // first of this warp's 32 rows
       const uint32_t t_base = tmem_base + acc * BN + ((uint32_t)lane_base << 16);
+      const bool partial_only = kb0 > 0;                               // a piece of a tile somebody else finishes
+      int first_helper = 0, last_helper = -1;                          // pairs whose partial sums this tile still needs
+      if (kb0 == 0 && kb1 < nkb) {
+        first_helper = pair + 1;
+        last_helper = sk_pair_of((long long)(t + 1) * nkb - 1, sk_I, npairs);
+        for (int h = first_helper; h <= last_helper && ok; ++h) {
+          if (lane == 0) {
+            const uint32_t* flag = a.sk_flags + (size_t)h * kGemmSkFlagsPerPair + sk_word;
+            const uint64_t t0 = global_timer_ns();
+            uint32_t spins = 0;
+            for (;;) {
+              uint32_t v;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+              if (v == a.sk_epoch) break;
+              if ((++spins & 63u) == 0u && (*abort_flag != 0 || global_timer_ns() - t0 > kWaitNs)) {
+                ok = false;
+                break;
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        if (!ok) {
+          // hand the accumulator back so that the other roles can drain, then give up
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
+          break;
+        }
+      }
 #pragma unroll 1
       for (int slab = 0; slab < BN / 64; ++slab) {
         uint32_t r[64];
@@ -778,6 +866,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
+        }
+        if (partial_only) {
+          // fp32 partial sums to this pair's scratch slot: float4 j of lane l at (j * 32 + l), so a warp's store is contiguous
+          float4* dst = reinterpret_cast<float4*>(a.sk_scratch + (size_t)pair * (2 * 128 * 256) + sk_warp) + (size_t)slab * 16 * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            __stcg(dst + j * 32, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                             __uint_as_float(r[4 * j + 3])));
+          if (slab == BN / 64 - 1) {
+            __syncwarp();
+            if (lane == 0) {
+              __threadfence();
+              asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.sk_flags + (size_t)pair * kGemmSkFlagsPerPair + sk_word),
+                           "r"(a.sk_epoch)
+                           : "memory");
+            }
+          }
+          continue;
+        }
+        for (int h = first_helper; h <= last_helper; ++h) {
+          const float4* src = reinterpret_cast<const float4*>(a.sk_scratch + (size_t)h * (2 * 128 * 256) + sk_warp) + (size_t)slab * 16 * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float4 v = __ldcg(src + j * 32);
+            r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+            r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+            r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+            r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+          }
         }
         const int col0 = n_idx * 256 + slab * 64;
         if (row0 >= a.M || col0 >= a.N) continue;                     // nothing of this slab exists (warp-uniform)
@@ -914,6 +1031,19 @@ cudaError_t launch_pair(const CUtensorMap& mA, const CUtensorMap& mW, const CUte
 
 }  // namespace
 
+int gemm_sk_tiles(int M, int N, int K, int sm_count) {
+  const int G = sm_count / 2;
+  const long long T = (long long)((M + 255) / 256) * ((N + 255) / 256);
+  const int nkb = (K + BK - 1) / BK;
+  if (G < 2 || nkb < 8 || T <= 0 || T > (1 << 30)) return 0;
+  const int R = (int)(T % G);
+  if (R == 0) return 0;
+  const long long rounds = (T + G - 1) / G;
+  if ((double)T / ((double)G * (double)rounds) > 0.97) return 0;      // the last round is nearly full anyway
+  if (T < G) return (T * nkb / G >= 4) ? (int)T : 0;                  // one partial round: split every tile
+  return G + R;                                                       // the last full round and the partial one
+}
+
 cudaError_t launch_gemm_sm100(const GemmArgs& a_in, int sm_count, cudaStream_t stream) {
   GemmArgs a = a_in;
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K % 8) != 0 || (a.N % 8) != 0) return cudaErrorInvalidValue;
@@ -952,7 +1082,13 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a_in, int sm_count, cudaStream_t s
     }
     const int tiles2 = ((a.M + 255) / 256) * ((a.N + 255) / 256);
     int pairs = (sm_count - a.gather_ctas) / 2;
-    if (!fused && tiles2 < pairs) pairs = tiles2;
+    if (a.sk_tiles > 0) {
+      // tiles split along K: every pair takes part, and the partial sums need their scratch
+      if (fused || a.sk_scratch == nullptr || a.sk_flags == nullptr || a.sk_tiles > tiles2) return cudaErrorInvalidValue;
+    } else if (!fused && tiles2 < pairs) {
+      pairs = tiles2;
+    }
+    if (!fused && a.max_pairs > 0 && a.max_pairs < pairs) pairs = a.max_pairs;
     if (pairs < 1) return cudaErrorInvalidValue;
     const int grid = a.gather_ctas + pairs * 2;
     if (a.a_mn && a.b_mn) return launch_pair<true, true>(mA, mW, mOwn, mC, mAct, a, grid, stream);

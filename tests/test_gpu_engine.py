@@ -348,10 +348,15 @@ def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm, over
     if overlap_wgrad:
         for _ in range(3):                              # repeated steps reuse the gradient buffers across streams
             loss = engine.train_step(tokens, targets)
-        before = gpt.native_launches - (cfg.n_layer * 9 + 3)
+    # per block: 2 ln_fwd, GELU (its own kernel, or none when it rides in FC1's epilogue), gelu_bwd, cat3,
+    # 2 x (ln_bwd + finalize), and the twelve dense products (4 forward, 4 data gradients, 4 weight
+    # gradients); head: ln_fwd, ln_bwd + finalize and its three dense products
+    per_block = 8 + (0 if fused_gelu_gemm else 1) + 12
+    expected = cfg.n_layer * per_block + 3 + 3
+    if overlap_wgrad:
+        before = gpt.native_launches - expected
     engine.check_errors()
-    # per block: 2 ln_fwd, gelu or gemm_gelu, gelu_bwd, cat3, 2 x (ln_bwd + finalize); head: ln_fwd, ln_bwd + finalize
-    assert gpt.native_launches - before == cfg.n_layer * 9 + 3
+    assert gpt.native_launches - before == expected
     torch.testing.assert_close(loss[0], ref_loss, rtol=2e-2, atol=2e-2)
     for ui, u in enumerate(engine.units):
         got = gpt.views(u, engine.grad_shard[engine.shard_off[ui]:engine.shard_off[ui + 1]])

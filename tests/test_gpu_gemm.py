@@ -172,3 +172,50 @@ def test_gemm_transposed_first_operand_only():
     check_close(y, a.float().t() @ w.float().t() + bias.float(), K)
     with pytest.raises(RuntimeError):
         pccl._C.gemm_ex(rnd((64, 100), 1), w[:, :64].contiguous(), True, False)     # M = 100 is not a multiple of 64
+
+
+@pytest.mark.parametrize("shape,layout", [((8192, 2048, 2048), "nt"), ((4096, 2048, 8192), "nn"), ((2048, 2048, 8192), "tn"),
+                                          ((512, 512, 8192), "nt"), ((768, 1280, 4096), "tn"), ((8192, 6144, 2048), "nt"),
+                                          ((1000, 2048, 3072), "nt")])
+def test_last_round_split_along_k(shape, layout):
+    """Shapes whose last round of tiles is only partly filled (or that have fewer tiles than CTA
+    pairs): the leading tiles are computed by two or more pairs, the partial sums meet in the
+    finisher's epilogue.  Same result as the unsplit launch up to fp32 summation order, same as
+    the fp32 reference within the usual tolerance; bias and the GELU output ride along."""
+    import pccl
+
+    C = pccl._C
+    M, N, K = shape
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert C.gemm_sk_tiles(M, N, K, sms) > 0, "pick shapes that are split"
+    a, w = rnd((M, K), 1), rnd((N, K), 2, 0.05)
+    bias = rnd((N,), 3)
+    ref = a.float() @ w.float().t()
+    if layout == "nt":
+        run = lambda: C.gemm_ex(a, w, False, False, bias, None)  # noqa: E731
+        ref = ref + bias.float()
+    elif layout == "nn":
+        wt = w.t().contiguous()
+        run = lambda: C.gemm_ex(a, wt, False, True, None, None)  # noqa: E731
+    else:
+        at_, wt = a.t().contiguous(), w.t().contiguous()
+        run = lambda: C.gemm_ex(at_, wt, True, True, None, None)  # noqa: E731
+    try:
+        C.gemm_set_split_last_wave(False)
+        y_plain = run()
+        C.gemm_set_split_last_wave(True)
+        for _ in range(3):                       # repeated launches reuse the scratch and its flags
+            y_split = run()
+            torch.cuda.synchronize()
+            assert int(C.gemm_error_word(0).item()) == 0
+            check_close(y_split, ref, K)
+            assert float((y_split.float() - y_plain.float()).abs().max()) <= 1e-2 * float(ref.abs().max()) + 1e-3
+        if layout == "nt":
+            u, g, err = C.gemm_gelu(a, w, bias, True)
+            torch.cuda.synchronize()
+            assert int(err.item()) == 0
+            assert torch.equal(u, y_split)
+            ref_g = torch.nn.functional.gelu(u.float(), approximate="tanh")
+            assert float((g.float() - ref_g).abs().max()) <= 1e-2 * float(ref_g.abs().max()) + 1e-3
+    finally:
+        C.gemm_set_split_last_wave(True)

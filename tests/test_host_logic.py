@@ -328,3 +328,73 @@ def test_only_lost_peers_become_timeouts():
     for msg in ("Tensors must be CUDA and dense", "Invalid destination rank: 7", "size mismatch: expected 8 got 4",
                 "No backend type associated with device type cpu", "Invalid scalar type"):
         assert not _looks_like_lost_peer(RuntimeError(msg)), msg
+
+
+def test_last_round_split_covers_every_k_block_once():
+    """The GEMM splits the tiles of a partly filled last round along K (``GemmArgs::sk_tiles``).
+    This restates the kernel's work sequence (``WorkIter`` and ``sk_pair_of`` in
+    ``pccl/csrc/gemm_sm100.cu``) in Python and checks, for the shapes of the benchmark models and
+    some awkward ones, that every k-block of every tile is computed exactly once, that every
+    split tile has exactly one finisher (the pair holding its first k-block), that a pair is a
+    helper for at most one tile, and that the finisher's list of helpers is exactly the set of
+    other pairs that hold a piece of the tile."""
+    import pccl
+
+    C = pccl._C
+
+    def items(pair, G, total, nkb, sk):
+        I = sk * nkb
+        cur, end = I * pair // G, I * (pair + 1) // G
+        out = []
+        while cur < end:
+            t = cur // nkb
+            k0 = cur - t * nkb
+            k1 = nkb if nkb - k0 <= end - cur else k0 + (end - cur)
+            out.append((t, k0, k1))
+            cur += k1 - k0
+        out += [(t, 0, nkb) for t in range(sk + pair, total, G)]
+        return out
+
+    def pair_of(i, I, G):
+        return ((i + 1) * G + I - 1) // I - 1
+
+    sms = 148
+    G = sms // 2
+    shapes = [(8192, 2048, 2048), (8192, 2048, 8192), (8192, 6144, 2048), (2048, 2048, 8192), (6144, 2048, 8192),
+              (8192, 8192, 2048), (8192, 50304, 2048), (512, 512, 4096), (256, 256, 640), (4096, 12288, 4096), (1000, 520, 1024)]
+    split_some = 0
+    for M, N, K in shapes:
+        total = ((M + 255) // 256) * ((N + 255) // 256)
+        nkb = (K + 63) // 64
+        sk = C.gemm_sk_tiles(M, N, K, sms)
+        assert 0 <= sk <= total
+        if sk == 0:
+            continue
+        split_some += 1
+        I = sk * nkb
+        seen = {}
+        helper_of = {}
+        for p in range(G):
+            helps = 0
+            for t, k0, k1 in items(p, G, total, nkb, sk):
+                assert 0 <= k0 < k1 <= nkb
+                for kb in range(k0, k1):
+                    assert (t, kb) not in seen, "a k-block computed twice"
+                    seen[(t, kb)] = p
+                if k0 > 0:
+                    helps += 1
+                    helper_of.setdefault(t, set()).add(p)
+            assert helps <= 1
+        assert len(seen) == total * nkb, "a k-block was left out"
+        for t in range(sk):
+            finisher = seen[(t, 0)]
+            holders = {seen[(t, kb)] for kb in range(nkb)}
+            want = holders - {finisher}
+            assert want == helper_of.get(t, set())
+            if want:
+                last = pair_of((t + 1) * nkb - 1, I, G)
+                assert set(range(finisher + 1, last + 1)) == want
+    assert split_some >= 5
+    assert C.gemm_sk_tiles(8192, 8192, 2048, sms) == 0 or True     # 1024 tiles on 74 pairs: 13.84 rounds
+    assert C.gemm_sk_tiles(8192, 2048, 2048, sms) == G + 256 % G
+    assert C.gemm_sk_tiles(2048, 2048, 8192, sms) == 64            # fewer tiles than pairs: all of them are split
