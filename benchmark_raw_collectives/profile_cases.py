@@ -5,7 +5,7 @@
     python benchmark_raw_collectives/profile_cases.py reduce_scatter
     python benchmark_raw_collectives/profile_cases.py adamw
     python benchmark_raw_collectives/profile_cases.py cross_entropy
-    python benchmark_raw_collectives/profile_cases.py gemm_nn | gemm_tn | gemm_split
+    python benchmark_raw_collectives/profile_cases.py gemm_nn | gemm_tn | gemm_split | cublas_gemm
     python benchmark_raw_collectives/profile_cases.py all_gather_ring | all_gather_recursive
     python benchmark_raw_collectives/profile_cases.py reduce_scatter_ring | reduce_scatter_recursive
     python benchmark_raw_collectives/profile_cases.py all_reduce | all_reduce_ring | broadcast
@@ -37,6 +37,17 @@ def gemm():
     out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
     for _ in range(3):
         pccl._C.gemm(A, W, None, out)
+    torch.cuda.synchronize()
+
+
+def cublas_gemm():
+    """The library kernel on the same product, for a side-by-side reading of the counters."""
+    M, N, K = 8192, 6144, 2048
+    A = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    W = (torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(3):
+        torch.matmul(A, W.t(), out=out)
     torch.cuda.synchronize()
 
 
@@ -205,7 +216,7 @@ def col_sum():
 
 
 CASES = {
-    "gemm": gemm, "gemm_nn": gemm_nn, "gemm_tn": gemm_tn, "gemm_split": gemm_split,
+    "gemm": gemm, "cublas_gemm": cublas_gemm, "gemm_nn": gemm_nn, "gemm_tn": gemm_tn, "gemm_split": gemm_split,
     "all_gather": all_gather, "all_gather_ring": lambda: _ag(sch.RING), "all_gather_recursive": lambda: _ag(sch.RECURSIVE),
     "reduce_scatter": reduce_scatter, "reduce_scatter_ring": lambda: _rs(sch.RING),
     "reduce_scatter_recursive": lambda: _rs(sch.RECURSIVE),

@@ -65,6 +65,21 @@ __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// The same for waits that are expected to last microseconds: pauses between polls.
+__device__ __forceinline__ bool gemm_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t it = 0;
+  for (;;) {
+    __nanosleep(64);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++it & 63u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > kWaitNs) return false;
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
@@ -673,7 +688,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   // Tiles are walked in bands: `group` row-tiles deep and all column-tiles wide (or, transposed,
   // `group` column-tiles wide and all row-tiles deep), down the short side of the band first.
   const bool walk_n = !fused && a.group_m < 0;            // bands of column-tiles
-  const int want = a.group_m > 0 ? a.group_m : (a.group_m < 0 ? -a.group_m : 8);
+  // Default depth of a band, from timings of the training shapes with a cold L2: long contractions
+  // run up to a fifth faster with shallow bands (the pairs of a round then share few row-tiles and
+  // write long contiguous runs of C), outputs that are much taller than wide want deep ones.
+  const int auto_depth = tiles_m > 4 * tiles_n ? 16 : (a.K >= 4096 ? 2 : 8);
+  const int want = a.group_m > 0 ? a.group_m : (a.group_m < 0 ? -a.group_m : auto_depth);
   const int major = walk_n ? tiles_n : tiles_m, minor = walk_n ? tiles_m : tiles_n;
   const int group = fused ? tiles_m : (major < want ? major : want);
   const int nkb = (a.K + BK - 1) / BK;
@@ -818,10 +837,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       int m_idx, n_idx;
       decode(t, &m_idx, &n_idx);
       const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
-      if (!gemm_wait(tmem_full + acc, acc_ph, abort_flag)) {
-        ok = false;
-        break;
-      }
+      // one lane polls the barrier (with a pause between polls: an accumulator takes microseconds),
+      // the others wait at the shuffle: 124 fewer threads hammering shared memory beside the MMAs
+      if (lane == 0) ok = gemm_wait_relaxed(tmem_full + acc, acc_ph, abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
       tc_fence_after();
       const int row0 = m_idx * 256 + (int)rank * 128 + lane_base;     // first of this warp's 32 rows
       const uint32_t t_base = tmem_base + acc * BN + ((uint32_t)lane_base << 16);
