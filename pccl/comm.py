@@ -40,6 +40,8 @@ _COLL_NAMES = {1: "all_gather", 2: "reduce_scatter", 3: "all_reduce", 4: "broadc
 DEFAULT_HEAP_BYTES = 1 << 30
 DEFAULT_SIG_BYTES = 4 << 20
 DEFAULT_STAGING_BYTES = 256 << 20
+_GUARD_BYTES = 256      # canary bytes on either side of a guarded symmetric tensor
+_GUARD_VALUE = 0xA5
 
 
 def _env_int(name: str, default: int) -> int:
@@ -114,6 +116,8 @@ class Communicator:
         self._groups: List[Group] = []
         self.world_group: Optional[Group] = None
         self._side_stream = None
+        self._guards = os.environ.get("PCCL_DEBUG", "0") == "1"     # canary bytes around symmetric tensors
+        self._guarded: List[Any] = []
         self._closed = False
         self.nvls = False
 
@@ -409,15 +413,50 @@ class Communicator:
         for s in shape:
             numel *= s
         nbytes = max(1, numel * torch.empty((), dtype=dtype).element_size())
-        off = self.native.alloc(nbytes, 256)
+        guard = _GUARD_BYTES if self._guards else 0
+        off = self.native.alloc(nbytes + 2 * guard, 256)
         if off < 0:
             raise PcclError(
                 f"symmetric heap exhausted: wanted {nbytes} bytes, {self.native.heap_used} of "
                 f"{self.native.heap_bytes} in use (set PCCL_HEAP_BYTES)")
         owners = list(range(self.world)) if self.emulated else [self.rank]
         # the storage of these tensors returns the block to the allocator when it dies
-        tensors = [t.view(shape) for t in self.native.owned_tensors(off, numel, dtype, owners)]
+        if not guard:
+            tensors = [t.view(shape) for t in self.native.owned_tensors(off, numel, dtype, owners)]
+            return tensors if self.emulated else tensors[0]
+        # Guarded allocation: 256 canary bytes in front of and behind the tensor.  A kernel that
+        # writes outside a buffer by up to 256 bytes changes them, and check_guards() says which
+        # buffer it was.  The user's tensor is a view into the middle of the owning byte tensor.
+        raw = self.native.owned_tensors(off, nbytes + 2 * guard, torch.uint8, owners)
+        tensors = []
+        for r, b in zip(owners, raw):
+            b[:guard].fill_(_GUARD_VALUE)
+            b[guard + nbytes:].fill_(_GUARD_VALUE)
+            t = b[guard:guard + numel * torch.empty((), dtype=dtype).element_size()].view(dtype).view(shape)
+            self._guarded.append((weakref.ref(t), r, off, nbytes))
+            tensors.append(t)
         return tensors if self.emulated else tensors[0]
+
+    def check_guards(self) -> None:
+        """With guard words on (``set_debug(guards=True)`` or ``PCCL_DEBUG=1``): synchronise and
+        verify the canary bytes around every live symmetric tensor of this process; raise
+        ``PcclError`` naming the first buffer whose surroundings were overwritten."""
+        if self.native is None or not self._guarded:
+            return
+        torch.cuda.synchronize(self.device)
+        alive = []
+        for ref, r, off, nbytes in self._guarded:
+            if ref() is None:
+                continue
+            alive.append((ref, r, off, nbytes))
+            front = self.native.tensor(off, _GUARD_BYTES, torch.uint8, r)
+            back = self.native.tensor(off + _GUARD_BYTES + nbytes, _GUARD_BYTES, torch.uint8, r)
+            for name, g in (("in front of", front), ("behind", back)):
+                if not bool((g == _GUARD_VALUE).all()):
+                    bad = int((g != _GUARD_VALUE).nonzero()[0])
+                    raise PcclError(f"guard bytes {name} the symmetric tensor at heap offset {off + _GUARD_BYTES} "
+                                    f"({nbytes} bytes, rank {r}) were overwritten (first at byte {bad})")
+        self._guarded = alive
 
     def is_symmetric(self, t: torch.Tensor) -> bool:
         if self.native is None or not t.is_cuda:
@@ -448,7 +487,7 @@ class Communicator:
                 raise PcclPoisonedError(msg)
 
     # ------------------------------------------------------------------ debugging aids
-    def set_debug(self, jitter_us: float = 0.0, trace_events: int = 0) -> None:
+    def set_debug(self, jitter_us: float = 0.0, trace_events: int = 0, guards: Optional[bool] = None) -> None:
         """Stress mode and device-side trace, both off by default.
 
         ``jitter_us`` > 0: every lane of every kernel of this communicator sleeps a pseudo-random
@@ -459,6 +498,10 @@ class Communicator:
         ``trace()`` reads them.  Also set from ``PCCL_DEBUG_JITTER_US`` / ``PCCL_TRACE_EVENTS``
         when the communicator is created.  The reference has neither: its only hook is
         ``record_function`` around benchmark iterations (``benchmark_raw_collectives/utils.py:20,27``)."""
+        if guards is not None:
+            # canary bytes around every symmetric tensor allocated from now on (``PCCL_DEBUG=1`` sets
+            # this from the start); ``check_guards()`` verifies them on the host
+            self._guards = bool(guards)
         if self.native is None:
             return
         torch.cuda.synchronize(self.device)

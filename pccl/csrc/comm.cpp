@@ -265,8 +265,26 @@ int Comm::clamp_lanes(int nlanes, const GroupState& gs) const {
   return std::max(1, std::min(nlanes, cap));
 }
 
+// Every address a kernel forms inside a peer's heap is "offset given by the host + something the
+// kernel derives from the sizes"; the largest such address is checked here, on the host, before
+// anything is launched, so a wrong offset or stride becomes an exception instead of a stray
+// store into a neighbour's buffer (the memory checker of the toolkit cannot be used on the pool).
+void Comm::check_extent(uint64_t off, uint64_t bytes, const char* what) const {
+  if (off > heap_bytes_ || bytes > heap_bytes_ - off)
+    throw Error(std::string(what) + ": the range [" + std::to_string(off) + ", +" + std::to_string(bytes) +
+                ") leaves the symmetric heap of " + std::to_string(heap_bytes_) + " bytes");
+}
+
 void Comm::all_gather(int gid, AllGatherArgs a, int nlanes, cudaStream_t stream) {
   if (a.algo == kMultimem && mc_heap_ == 0) throw Error("multimem all-gather requested but no multicast mapping exists");
+  {
+    const uint64_t P = (uint64_t)group_size(gid), ns = (uint64_t)(a.nsub > 0 ? a.nsub - 1 : 0);
+    if (a.algo == kPull) {
+      check_extent(a.in_off, ns * a.in_sub_stride + a.sub_bytes, "all-gather (pull) input slot");
+    } else if (P > 1) {
+      check_extent(a.recv_off, (P - 1) * a.src_stride + ns * a.sub_stride + a.sub_bytes, "all-gather landing zone");
+    }
+  }
   if (a.algo == kRecursive && !is_pow2(group_size(gid))) throw Error("recursive doubling needs a power-of-two group");
   // user tensors never lie inside the staging area (the allocator has reserved it), so an offset
   // there means staging; pull leaves recv_off unused and stages only a private input
@@ -278,6 +296,15 @@ void Comm::all_gather(int gid, AllGatherArgs a, int nlanes, cudaStream_t stream)
 void Comm::reduce_scatter(int gid, ReduceScatterArgs a, int nlanes, cudaStream_t stream) {
   if (a.algo == kMultimem && mc_heap_ == 0) throw Error("multimem reduce-scatter requested but no multicast mapping exists");
   if (a.algo == kRecursive && !is_pow2(group_size(gid))) throw Error("recursive halving needs a power-of-two group");
+  {
+    const uint64_t P = (uint64_t)group_size(gid), ns = (uint64_t)(a.nsub > 0 ? a.nsub : 1);
+    if (a.algo == kPull || a.algo == kMultimem) {
+      check_extent(a.in_off, (P - 1) * a.dst_stride + (ns - 1) * a.sub_stride + a.sub_elems * (uint64_t)dtype_size(a.in_dtype),
+                   "reduce-scatter symmetric input");
+    } else if (P > 1) {
+      check_extent(a.stage_off, (P - 1) * ns * a.sub_elems * (uint64_t)dtype_size(a.wire_dtype), "reduce-scatter staging");
+    }
+  }
   const bool staged = a.algo != kPull && a.algo != kMultimem && in_staging(a.stage_off);
   begin_call(gid, &a.g, stream, staged);
   PCCL_CUDA(launch_reduce_scatter(a, clamp_lanes(nlanes, groups_[gid]), stream));
@@ -285,6 +312,7 @@ void Comm::reduce_scatter(int gid, ReduceScatterArgs a, int nlanes, cudaStream_t
 
 void Comm::all_reduce(int gid, AllReduceArgs a, int nlanes, cudaStream_t stream) {
   if (a.algo == kMultimem && mc_heap_ == 0) throw Error("multimem all-reduce requested but no multicast mapping exists");
+  if (group_size(gid) > 1) check_extent(a.buf_off, a.elems * (uint64_t)dtype_size(a.dtype), "all-reduce working buffer");
   begin_call(gid, &a.g, stream, in_staging(a.buf_off));
   PCCL_CUDA(launch_all_reduce(a, clamp_lanes(nlanes, groups_[gid]), stream));
 }
@@ -293,6 +321,11 @@ void Comm::all_reduce_rsag(int gid, AllReduceRsAgArgs a, int nlanes, cudaStream_
   if (a.rs.algo != a.ag.algo || (a.rs.algo != kRing && a.rs.algo != kRecursive))
     throw Error("the two-phase all-reduce runs the ring or the recursive schedules");
   if (a.rs.algo == kRecursive && !is_pow2(group_size(gid))) throw Error("recursive halving/doubling needs a power-of-two group");
+  {
+    const uint64_t P = (uint64_t)group_size(gid);
+    check_extent(a.rs.stage_off, (P - 1) * a.rs.sub_elems * (uint64_t)dtype_size(a.rs.wire_dtype), "all-reduce staging of partial sums");
+    check_extent(a.ag.recv_off, (P - 1) * a.ag.src_stride + a.ag.sub_bytes, "all-reduce gather landing zone");
+  }
   const bool staged = in_staging(a.rs.stage_off) || in_staging(a.ag.recv_off);
   begin_call(gid, &a.rs.g, stream, staged);     // two call numbers: one per phase
   begin_call(gid, &a.ag.g, stream, staged);
@@ -302,6 +335,7 @@ void Comm::all_reduce_rsag(int gid, AllReduceRsAgArgs a, int nlanes, cudaStream_
 void Comm::broadcast(int gid, BroadcastArgs a, int nlanes, cudaStream_t stream) {
   if (a.use_multimem && mc_heap_ == 0) throw Error("multimem broadcast requested but no multicast mapping exists");
   if (a.root < 0 || a.root >= group_size(gid)) throw Error("broadcast root outside the group");
+  if (group_size(gid) > 1) check_extent(a.buf_off, a.bytes, "broadcast buffer");
   begin_call(gid, &a.g, stream, in_staging(a.buf_off));
   PCCL_CUDA(launch_broadcast(a, clamp_lanes(nlanes, groups_[gid]), stream));
 }

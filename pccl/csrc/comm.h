@@ -131,6 +131,7 @@ class Comm {
 
  private:
   int clamp_lanes(int nlanes, const GroupState& gs) const;
+  void check_extent(uint64_t off, uint64_t bytes, const char* what) const;
   bool in_staging(uint64_t off) const { return staging_bytes_ > 0 && off >= staging_off_ && off < staging_off_ + staging_bytes_; }
 
   int world_, rank_, nlocal_, device_;

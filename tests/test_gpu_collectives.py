@@ -468,3 +468,37 @@ def test_collectives_of_different_groups_share_the_staging_area_in_order():
             assert torch.equal(outs[r], torch.cat(ins)), f"all_gather rep {rep} rank {r}"
             torch.testing.assert_close(red[r], want[r], rtol=1e-5, atol=1e-5)
     comm.close()
+
+
+def test_guard_words_and_extent_checks():
+    """Debug aids that stand in for a memory checker: canary bytes around symmetric tensors, verified
+    on the host, and a host-side check that every landing zone a launch names lies inside the heap."""
+    comm = pccl.Communicator.emulated_world(4, device=0, heap_bytes=32 << 20, staging_bytes=4 << 20)
+    comm.set_debug(guards=True)
+    gid = comm.world_group.gid
+    n = 12345
+    outs = comm.empty(4 * n, torch.bfloat16)
+    sym_in = comm.empty(4 * n, torch.bfloat16)
+    vals = [rand(n, torch.bfloat16, 3 + r) for r in range(4)]
+    for algo in (sch.DIRECT, sch.RING, sch.RECURSIVE, sch.PULL):
+        comm.native.all_gather(gid, outs, vals, sch.ALGO_IDS[algo], 5)
+    for r in range(4):
+        sym_in[r].copy_(rand(4 * n, torch.bfloat16, 40 + r))
+    res = [torch.zeros(n, device=DEV) for _ in range(4)]
+    for algo in (sch.DIRECT, sch.RING, sch.RECURSIVE, sch.PULL):
+        comm.native.reduce_scatter(gid, res, sym_in, sch.ALGO_IDS[algo], 5, 1.0, None)
+    comm.native.all_reduce(gid, outs, sch.ALGO_IDS[sch.RING], 4, 1.0)
+    comm.check()
+    comm.check_guards()                                   # nothing wrote outside its buffer
+    assert torch.equal(outs[0], outs[3])
+    # a stray write just behind a buffer is found and attributed
+    off = comm.native.offset_of(outs[2].data_ptr(), outs[2].numel() * 2, 2)
+    comm.native.tensor(off + 4 * n * 2 + 7, 1, torch.uint8, 2).fill_(0)
+    with pytest.raises(pccl.PcclError, match="behind"):
+        comm.check_guards()
+    # a landing zone that leaves the heap is refused before anything is launched
+    with pytest.raises(RuntimeError, match="leaves the symmetric heap"):
+        ag2d_outer_call(comm.native, gid, sch.ALGO_IDS[sch.RING], 2, [v.data_ptr() for v in vals], (32 << 20) - 1000, 0,
+                        n * 2, 1)
+    comm.check()
+    comm.close()
