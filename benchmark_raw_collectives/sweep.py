@@ -148,7 +148,11 @@ def main() -> None:
         rec = {"sweep": sweep, "collective": collective, "P": world, "dtype": str(dtype).replace("torch.", ""),
                "per_rank_bytes": nbytes, "nccl_ms": round(ms_nccl, 5), "nccl_busbw_gbs": round(busbw(ms_nccl), 2),
                "variants": {}}
-        for a in variants(collective):
+        names = variants(collective)
+        cap = comm.native.eager_capacity
+        if args.algorithms == "all" and cap > 0 and (world * nbytes if collective == "all_gather" else (world - 1) * wire) <= cap:
+            names = names + [sch.EAGER]
+        for a in names:
             fn = ours(a)
             ms = time_something(fn, warmup_iters=args.warmup, timed_iters=args.iters)
             comm.check()
@@ -214,7 +218,9 @@ def markdown(doc: Dict) -> str:
     for r in doc["rows"]:
         by_sweep.setdefault(r["sweep"], []).append(r)
     for sweep, rs in by_sweep.items():
-        names = list(rs[0]["variants"].keys())
+        names = []
+        for r in rs:                                     # some variants (eager) only exist at small sizes
+            names += [a for a in r["variants"] if a not in names]
         out.append(f"### {sweep} ({rs[0]['collective']}, {rs[0]['dtype']})")
         out.append("")
         out.append("| per-rank MiB | NCCL µs | NCCL GB/s | " + " | ".join(f"{a} µs" for a in names) +
@@ -223,8 +229,8 @@ def markdown(doc: Dict) -> str:
         for r in rs:
             b, p = r.get("best", {}), r.get("best_without_multimem", {})
             cells = [f"{r['per_rank_bytes'] / (1 << 20):g}", f"{r['nccl_ms'] * 1e3:.1f}", f"{r['nccl_busbw_gbs']:.1f}"]
-            cells += [f"{r['variants'][a]['ms'] * 1e3:.1f}" + ("" if r['variants'][a]['correct'] in (None, True) else " (WRONG)")
-                      for a in names]
+            cells += [(f"{r['variants'][a]['ms'] * 1e3:.1f}" + ("" if r['variants'][a]['correct'] in (None, True) else " (WRONG)"))
+                      if a in r["variants"] else "-" for a in names]
             cells += [b.get("variant", "-"), f"{b.get('busbw_gbs', 0):.1f}", f"{b.get('vs_nccl', 0)}", f"{b.get('frac_of_900', 0):.2f}",
                       p.get("variant", "-"), f"{p.get('busbw_gbs', 0):.1f}", f"{p.get('vs_nccl', 0)}"]
             out.append("| " + " | ".join(cells) + " |")

@@ -82,7 +82,8 @@ def _all_gather(output_tensor: torch.Tensor, input_tensor: torch.Tensor,
         algo, nl = tuner.choose("all_gather", group.size, nbytes, requested=algo,
                                 symmetric_in=comm.is_symmetric(input_tensor),
                                 symmetric_out=comm.is_symmetric(output_tensor),
-                                has_multimem=comm.nvls, lanes=lanes, max_lanes=comm.native.max_lanes)
+                                has_multimem=comm.nvls, lanes=lanes, max_lanes=comm.native.max_lanes,
+                                eager_capacity=comm.native.eager_capacity if group.gid == 0 else 0)
         if algo == sch.MULTIMEM and not comm.is_symmetric(output_tensor):
             algo = sch.DIRECT
         native = comm.native
@@ -154,8 +155,8 @@ def _all_gather_2d_native(out, inp, inner: Group, outer: Group, intra: int, inte
     out_ptr = 0 if out_off >= 0 else out.data_ptr()
     a1, l1 = tuner.choose("all_gather", inter, n, requested=algo, lanes=lanes, max_lanes=native.max_lanes)
     a2, l2 = tuner.choose("all_gather", intra, n * inter, requested=algo, lanes=lanes, max_lanes=native.max_lanes)
-    a1 = sch.DIRECT if a1 in (sch.PULL, sch.MULTIMEM) else a1
-    a2 = sch.DIRECT if a2 in (sch.PULL, sch.MULTIMEM) else a2
+    a1 = sch.DIRECT if a1 in (sch.PULL, sch.MULTIMEM, sch.EAGER) else a1
+    a2 = sch.DIRECT if a2 in (sch.PULL, sch.MULTIMEM, sch.EAGER) else a2
 
     def launch():
         ag2d_outer_call(native, outer.gid, sch.ALGO_IDS[a1], l1, [inp.data_ptr()], recv_off, i, n, intra)

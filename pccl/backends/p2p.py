@@ -81,7 +81,7 @@ def all_gather(out: torch.Tensor, inp: torch.Tensor, tr: P2PTransport, algo: str
     n = inp.numel()
     if out.numel() != P * n:
         raise ValueError(f"output has {out.numel()} elements, expected {P}*{n}")
-    if algo in (sch.PULL, sch.MULTIMEM):
+    if algo in (sch.PULL, sch.MULTIMEM, sch.EAGER):
         algo = sch.DIRECT
     sch.check_algo(algo, P)
     blocks = out.view(-1).view(P, n)
@@ -103,7 +103,7 @@ def reduce_scatter(out: torch.Tensor, inp: torch.Tensor, tr: P2PTransport, algo:
     n = inp.numel() // P
     if out.numel() != n:
         raise ValueError(f"output has {out.numel()} elements, expected {n}")
-    if algo in (sch.PULL, sch.MULTIMEM):
+    if algo in (sch.PULL, sch.MULTIMEM, sch.EAGER):
         algo = sch.DIRECT
     sch.check_algo(algo, P)
     wire = wire_dtype or inp.dtype

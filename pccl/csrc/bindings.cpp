@@ -105,6 +105,26 @@ void all_gather(Comm& c, int gid, std::vector<at::Tensor> outs, std::vector<at::
   a.in_sub_stride = n;
   if (algo == kMultimem) TORCH_CHECK(n % 16 == 0, "multimem all-gather needs a multiple of 16 bytes per rank");
 
+  if (algo == kEager) {
+    // Small messages on the world group: the direct schedule into this call's half of the eager
+    // area, no entry handshake; the result is copied out of the area by the same kernel.
+    TORCH_CHECK(gid == 0, "the eager variant runs on the world group only");
+    TORCH_CHECK(c.eager_capacity() >= (uint64_t)P * n, "message too large for the eager area: ", P * n, " bytes, capacity ",
+                c.eager_capacity());
+    const uint64_t slot = c.eager_capacity() / (uint64_t)P / 16 * 16;
+    a.algo = kDirect;
+    a.eager = 1;
+    a.recv_off = c.next_eager_half();
+    a.src_stride = slot;
+    a.sub_bytes = n;
+    for (int i = 0; i < l.n; ++i) {
+      a.in[i] = (const char*)ins[i].data_ptr();
+      a.out[i] = (char*)outs[i].data_ptr();
+    }
+    c.all_gather(gid, a, nlanes, stream);
+    return;
+  }
+
   if (algo == kPull) {
     // Results go straight to the outputs; only a private input needs staging.
     uint64_t cap = n;
@@ -276,6 +296,23 @@ void reduce_scatter(Comm& c, int gid, std::vector<at::Tensor> outs, std::vector<
     a.sub_elems = n;
     for (int i = 0; i < l.n; ++i) {
       a.in[i] = nullptr;
+      a.out[i] = (char*)outs[i].data_ptr();
+    }
+    c.reduce_scatter(gid, a, nlanes, stream);
+    return;
+  }
+
+  if (algo == kEager) {
+    // Small messages on the world group: every rank pushes block d of its input into rank d's half
+    // of the eager area (no entry handshake) and sums what it received.
+    TORCH_CHECK(gid == 0, "the eager variant runs on the world group only");
+    TORCH_CHECK(P == 1 || c.eager_capacity() >= (uint64_t)(P - 1) * n * sw, "message too large for the eager area");
+    a.algo = kDirect;
+    a.eager = 1;
+    a.stage_off = c.next_eager_half();
+    a.sub_elems = n;
+    for (int i = 0; i < l.n; ++i) {
+      a.in[i] = (const char*)ins[i].data_ptr();
       a.out[i] = (char*)outs[i].data_ptr();
     }
     c.reduce_scatter(gid, a, nlanes, stream);
@@ -604,6 +641,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("RECURSIVE") = (int)kRecursive;
   m.attr("PULL") = (int)kPull;
   m.attr("MULTIMEM") = (int)kMultimem;
+  m.attr("EAGER") = (int)kEager;
   m.attr("STATUS_OK") = (int)kStatusOk;
   m.attr("STATUS_TIMEOUT") = (int)kStatusTimeout;
   m.attr("STATUS_POISONED") = (int)kStatusPoisoned;
@@ -683,6 +721,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("staging_off", &Comm::staging_off)
       .def_property_readonly("staging_bytes", &Comm::staging_bytes)
       .def_property_readonly("max_lanes", &Comm::max_lanes)
+      .def_property_readonly("eager_capacity", &Comm::eager_capacity,
+                             "bytes of one half of the eager area (0: none): an eager all-gather needs P * bytes per rank, "
+                             "an eager reduce-scatter (P-1) * bytes per block")
       .def_property_readonly("kernels_launched", &Comm::kernels_launched)
       .def("heap_base", &Comm::heap_base)
       .def("alloc", &Comm::alloc, py::arg("bytes"), py::arg("align") = 256)

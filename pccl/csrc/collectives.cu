@@ -154,8 +154,13 @@ __device__ __forceinline__ void all_gather_body(const AllGatherArgs& a, BulkPipe
     if (!cta_wait_mask(g, c, kSlotStep0, others)) return;
   } else if (algo == kDirect) {
     // One pass over the own block feeds every peer (and the local copies) from one staging read.
-    cta_signal_mask(g, c, kSlotEntry, others);
-    if (!cta_wait_mask(g, c, kSlotEntry, others)) return;
+    // Eager calls land in the half of the eager area that no peer can still be reading (it was last
+    // used two eager calls ago, and every peer has since been seen in the call in between), so they
+    // need no handshake before the first store.
+    if (!a.eager) {
+      cta_signal_mask(g, c, kSlotEntry, others);
+      if (!cta_wait_mask(g, c, kSlotEntry, others)) return;
+    }
     for (int j = 0; j < a.nsub; ++j) {
       char* dsts[kMaxRanks + 1];
       int nd = 0;
@@ -344,9 +349,10 @@ __device__ __forceinline__ void reduce_scatter_body(const ReduceScatterArgs& a, 
     return;
   }
 
-  // Push schedules: partial sums travel in the wire dtype, fp32 in registers.
-  cta_signal_mask(g, c, kSlotEntry, others);
-  unsigned entered = 0, arrived = 0;
+  // Push schedules: partial sums travel in the wire dtype, fp32 in registers.  Eager calls (direct
+  // schedule into this call's half of the eager area) skip the entry handshake.
+  if (!a.eager) cta_signal_mask(g, c, kSlotEntry, others);
+  unsigned entered = a.eager ? ~0u : 0u, arrived = 0;
   const int n = num_steps(algo, P);
   for (int t = 0; t <= n; ++t) {
     const unsigned deps = rs_dep_mask(algo, P, t);

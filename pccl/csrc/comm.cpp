@@ -91,6 +91,15 @@ Comm::Comm(int world, int rank, int nlocal, int device, std::vector<uint64_t> he
     staging_off_ = (uint64_t)off;
     staging_bytes_ = staging_bytes;
   }
+  // the eager area: at most 2 x 8 MiB, at most an eighth of the heap; none in very small heaps
+  uint64_t half = std::min<uint64_t>(8ull << 20, heap_bytes / 16) / 4096 * 4096;
+  if (world > 1 && half >= (64u << 10)) {
+    const int64_t off = allocator_.alloc(2 * half, 4096);
+    if (off >= 0) {
+      eager_off_ = (uint64_t)off;
+      eager_half_bytes_ = half;
+    }
+  }
 }
 
 Comm::~Comm() {
@@ -204,6 +213,7 @@ void Comm::reset_after_failure() {
     g.epoch = 0;
     g.used = false;
   }
+  eager_calls_ = 0;
   PCCL_CUDA(cudaDeviceSynchronize());
 }
 

@@ -82,6 +82,12 @@ class Comm {
   uint64_t staging_off() const { return staging_off_; }
   uint64_t staging_bytes() const { return staging_bytes_; }
   int max_lanes() const { return max_lanes_; }
+  // Eager area: two halves inside the heap, used alternately by the eager calls of the WORLD group
+  // (group 0).  eager_capacity() is the size of one half (0: no area); next_eager_half() returns the
+  // offset of the half the next eager call writes into and advances the alternation.  Every rank
+  // issues the same sequence of eager calls, so the ranks agree on the half.
+  uint64_t eager_capacity() const { return eager_half_bytes_; }
+  uint64_t next_eager_half() { return eager_off_ + (uint64_t)((eager_calls_++) & 1u) * eager_half_bytes_; }
 
   int64_t alloc(uint64_t bytes, uint64_t align = 256);
   void free(int64_t off);
@@ -138,6 +144,8 @@ class Comm {
   std::vector<uint64_t> heaps_, sigs_;
   uint64_t mc_heap_, heap_bytes_, sig_bytes_;
   uint64_t staging_off_ = 0, staging_bytes_ = 0;
+  uint64_t eager_off_ = 0, eager_half_bytes_ = 0;
+  uint64_t eager_calls_ = 0;
   cudaEvent_t staging_tail_ = nullptr;        // last launch that touched the staging area, on any group
   cudaStream_t staging_stream_ = nullptr;
   bool staging_used_ = false;

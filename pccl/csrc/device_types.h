@@ -115,6 +115,8 @@ struct AllGatherArgs {
   uint64_t in_sub_stride;       // distance between consecutive sub-blocks of `in` (and of the kPull staging)
   int nsub;
   uint64_t in_off;              // kPull: offset of the contribution inside the owner's heap
+  int eager;                    // direct schedule without the entry handshake: recv_off is the half of the eager
+                                // area that this call may overwrite (see Comm::eager_half)
 };
 
 // ------------------------------------------------------------------ reduce-scatter
@@ -134,6 +136,7 @@ struct ReduceScatterArgs {
   uint64_t out_sub_stride;      // bytes between consecutive sub-blocks of `out`
   int nsub;
   float scale;
+  int eager;                    // direct schedule without the entry handshake: stage_off is this call's half of the eager area
 };
 
 // ------------------------------------------------------------------ all-reduce (in place, two-shot)

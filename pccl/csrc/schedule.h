@@ -32,6 +32,8 @@ enum Algo : int {
   kRecursive = 2,  // log2(P) steps: doubling for all-gather, halving for reduce-scatter
   kPull = 3,       // direct, but the consumer loads from the peers' symmetric input
   kMultimem = 4,   // NVLS: multimem.st / multimem.ld_reduce through the switch
+  kEager = 5,      // small messages: the direct schedule into a double-buffered landing area of the
+                   // communicator, without the entry handshake (one flag trip instead of three)
 };
 
 struct Step {

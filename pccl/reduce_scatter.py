@@ -79,7 +79,10 @@ def _reduce_scatter(output_tensor: torch.Tensor, input_tensor: torch.Tensor,
         nbytes = output_tensor.numel() * input_tensor.element_size()
         algo, nl = tuner.choose("reduce_scatter", group.size, nbytes, requested=algo,
                                 symmetric_in=comm.is_symmetric(input_tensor), has_multimem=comm.nvls,
-                                lanes=lanes, max_lanes=comm.native.max_lanes)
+                                lanes=lanes, max_lanes=comm.native.max_lanes,
+                                eager_capacity=comm.native.eager_capacity if group.gid == 0 else 0)
+        if algo == sch.EAGER and wire_dtype == torch.float32 and input_tensor.dtype != torch.float32:
+            algo = sch.DIRECT            # fp32 wire doubles the landing bytes: keep the capacity rule simple
         native = comm.native
 
         def launch():
@@ -148,8 +151,8 @@ def _reduce_scatter_2d_native(out, inp, inner: Group, outer: Group, intra: int, 
     tin, tout = _DT[inp.dtype], _DT[out.dtype]
     a1, l1 = tuner.choose("reduce_scatter", intra, n * inter * es, requested=algo, lanes=lanes, max_lanes=native.max_lanes)
     a2, l2 = tuner.choose("reduce_scatter", inter, n * es, requested=algo, lanes=lanes, max_lanes=native.max_lanes)
-    a1 = sch.DIRECT if a1 in (sch.PULL, sch.MULTIMEM) else a1
-    a2 = sch.DIRECT if a2 in (sch.PULL, sch.MULTIMEM) else a2
+    a1 = sch.DIRECT if a1 in (sch.PULL, sch.MULTIMEM, sch.EAGER) else a1
+    a2 = sch.DIRECT if a2 in (sch.PULL, sch.MULTIMEM, sch.EAGER) else a2
     mid = torch.empty(inter * n, dtype=inp.dtype, device=inp.device)
 
     def launch():

@@ -24,7 +24,11 @@ AUTO = "auto"
 # caller guarantees that the peers' inputs do not change while the call is in flight
 COPY_ENGINE = "copy_engine"
 
-ALGO_IDS = {DIRECT: 0, RING: 1, RECURSIVE: 2, PULL: 3, MULTIMEM: 4}
+# small messages on the world group: the direct schedule into a double-buffered landing area of the
+# communicator without the entry handshake (one flag trip instead of three)
+EAGER = "eager"
+
+ALGO_IDS = {DIRECT: 0, RING: 1, RECURSIVE: 2, PULL: 3, MULTIMEM: 4, EAGER: 5}
 ALGO_NAMES = {v: k for k, v in ALGO_IDS.items()}
 MAX_RANKS = 8
 

@@ -56,8 +56,12 @@ def lookup(collective: str, world: int, nbytes: int) -> Optional[Tuple[List[str]
 
 
 def _feasible(collective: str, algo: str, world: int, nbytes: int, symmetric_in: bool, symmetric_out: bool,
-              has_multimem: bool) -> bool:
+              has_multimem: bool, eager_capacity: int = 0) -> bool:
     """Variants that read or multicast peer memory need the right tensors in the heap."""
+    if algo == sch.EAGER:
+        # eager_capacity is 0 unless the call is on the world group of a communicator with an eager area
+        need = world * nbytes if collective == "all_gather" else (world - 1) * nbytes
+        return collective in ("all_gather", "reduce_scatter") and 0 < need <= eager_capacity
     if algo == sch.MULTIMEM:
         if not has_multimem or nbytes % 16 != 0:
             return False
@@ -74,7 +78,7 @@ def _feasible(collective: str, algo: str, world: int, nbytes: int, symmetric_in:
 
 def choose(collective: str, world: int, nbytes: int, *, requested: str = sch.AUTO, symmetric_in: bool = False,
            symmetric_out: bool = False, has_multimem: bool = False, lanes: Optional[int] = None,
-           max_lanes: int = DEFAULT_MAX_LANES) -> Tuple[str, int]:
+           max_lanes: int = DEFAULT_MAX_LANES, eager_capacity: int = 0) -> Tuple[str, int]:
     """Return ``(algorithm, nlanes)``.  ``nbytes`` is the per-rank block size."""
     env_algo = os.environ.get("PCCL_ALGO")
     env_lanes = os.environ.get("PCCL_LANES")
@@ -87,10 +91,10 @@ def choose(collective: str, world: int, nbytes: int, *, requested: str = sch.AUT
         candidates, picked_lanes = hit if hit is not None else ([sch.DIRECT], None)
         algo = sch.DIRECT
         for cand in candidates:
-            if _feasible(collective, cand, world, nbytes, symmetric_in, symmetric_out, has_multimem):
+            if _feasible(collective, cand, world, nbytes, symmetric_in, symmetric_out, has_multimem, eager_capacity):
                 algo = cand
                 break
-    elif not _feasible(collective, algo, world, nbytes, symmetric_in, symmetric_out, has_multimem):
+    elif not _feasible(collective, algo, world, nbytes, symmetric_in, symmetric_out, has_multimem, eager_capacity):
         if algo == sch.RECURSIVE and requested == sch.RECURSIVE:
             sch.check_algo(algo, world)   # raises: the caller asked for it explicitly
         algo = sch.DIRECT

@@ -502,3 +502,41 @@ def test_guard_words_and_extent_checks():
                         n * 2, 1)
     comm.check()
     comm.close()
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+def test_eager_small_messages(P):
+    """The handshake-free variant for small messages on the world group: direct schedule into the
+    alternating halves of the communicator's eager area.  Back-to-back calls of changing size (and
+    lane count), all-gather and reduce-scatter mixed, private and symmetric tensors, with stress
+    jitter: the halves must never be overwritten while a slower rank still reads them."""
+    comm = pccl.Communicator.emulated_world(P, device=0, heap_bytes=64 << 20, staging_bytes=8 << 20)
+    gid = comm.world_group.gid
+    cap = comm.native.eager_capacity
+    assert cap >= 1 << 20
+    E = sch.ALGO_IDS[sch.EAGER]
+    sym_out = comm.empty(P * 70000, torch.bfloat16)
+    for jitter in (0.0, 120.0):
+        comm.set_debug(jitter_us=jitter)
+        for rep, n in enumerate([1, 17, 4099, 70000, 33, 65536, 5]):
+            lanes = 1 + rep % 5
+            ins = [rand(n, torch.bfloat16, 1000 * rep + r) for r in range(P)]
+            outs = [torch.zeros(P * n, dtype=torch.bfloat16, device=DEV) for _ in range(P)] if rep % 2 == 0 else \
+                [t[:P * n] for t in sym_out]
+            comm.native.all_gather(gid, outs, ins, E, lanes)
+            big = [rand(P * n, torch.bfloat16, 7000 * rep + r) for r in range(P)]
+            res = [torch.zeros(n, dtype=torch.float32, device=DEV) for _ in range(P)]
+            comm.native.reduce_scatter(gid, res, big, E, lanes, 1.0 / P, None)
+            comm.check()
+            want = torch.cat(ins)
+            want_rs = rs_reference(big, P, n, 1.0 / P, torch.float32)
+            for r in range(P):
+                assert torch.equal(outs[r], want), f"eager all_gather P={P} n={n} rank {r}"
+                torch.testing.assert_close(res[r], want_rs[r], rtol=1e-5, atol=1e-5)
+    comm.set_debug(0.0, 0)
+    too_big = cap // P // 2 + 8
+    with pytest.raises(RuntimeError, match="eager area"):
+        comm.native.all_gather(gid, [torch.zeros(P * too_big, dtype=torch.bfloat16, device=DEV) for _ in range(P)],
+                               [torch.zeros(too_big, dtype=torch.bfloat16, device=DEV) for _ in range(P)], E, 2)
+    del sym_out
+    comm.close()
