@@ -139,6 +139,8 @@ def run_arm(args, impl: str, ctx: dict) -> dict:
     if library:
         if ctx.get("comm") is None:
             heap = heap_bytes_needed(cfg, world, bool(args.fused_ag_gemm)) + (320 << 20)
+            if not args.no_raw:
+                heap += 2304 << 20          # the 1 GiB points of the two raw-collective sweeps: output + input, or input
             ctx["comm"] = pccl.init(heap_bytes=heap, staging_bytes=64 << 20, enable_nvls=bool(args.nvls))
         comm = ctx["comm"]
         patch_deepspeed(world, algorithm=args.algorithm, lanes=args.lanes)

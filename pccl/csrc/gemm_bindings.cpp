@@ -206,30 +206,82 @@ CopyLane& copy_lane(int device) {
 }
 
 using WriteValue32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+using BatchMemOpFn = CUresult (*)(CUstream, unsigned int, CUstreamBatchMemOpParams*, unsigned int);
 
-WriteValue32Fn write_value32() {
-  static WriteValue32Fn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess || p == nullptr)
-      throw Error("this driver does not offer cuStreamWriteValue32 (stream memory operations)");
-    fn = reinterpret_cast<WriteValue32Fn>(p);
-  }
-  return fn;
+template <typename Fn>
+Fn driver_entry(const char* name) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return nullptr;
+  return reinterpret_cast<Fn>(p);
 }
 
-// Enqueue the copies and flag writes of one fused call on the device's copy stream, ordered after
-// everything `compute` has queued so far.  `panels_per_copy` <= 0: one copy per peer shard.
-void enqueue_copy_engine_gather(const GemmArgs& a, char* w_full, int panels_per_copy, cudaStream_t compute, int device) {
+// Write `value` into `count` consecutive 32-bit words at `first`, in stream order: one batched
+// stream memory operation where the driver offers it, else one write per word.
+void stream_write_words(cudaStream_t stream, uint32_t* first, int count, uint32_t value) {
+  static BatchMemOpFn batch = driver_entry<BatchMemOpFn>("cuStreamBatchMemOp");
+  static WriteValue32Fn single = driver_entry<WriteValue32Fn>("cuStreamWriteValue32");
+  if (count <= 0) return;
+  if (batch != nullptr && count > 1) {
+    CUstreamBatchMemOpParams ops[64];
+    for (int done = 0; done < count;) {
+      const int n = std::min(64, count - done);
+      std::memset(ops, 0, sizeof(CUstreamBatchMemOpParams) * n);
+      for (int i = 0; i < n; ++i) {
+        ops[i].writeValue.operation = CU_STREAM_MEM_OP_WRITE_VALUE_32;
+        ops[i].writeValue.address = reinterpret_cast<CUdeviceptr>(first + done + i);
+        ops[i].writeValue.value = value;
+        ops[i].writeValue.flags = CU_STREAM_WRITE_VALUE_DEFAULT;
+      }
+      const CUresult r = batch(reinterpret_cast<CUstream>(stream), (unsigned)n, ops, 0u);
+      if (r != CUDA_SUCCESS) throw Error("cuStreamBatchMemOp failed with code " + std::to_string((int)r));
+      done += n;
+    }
+    return;
+  }
+  if (single == nullptr) throw Error("this driver offers no stream memory operations (cuStreamWriteValue32)");
+  for (int i = 0; i < count; ++i) {
+    const CUresult r = single(reinterpret_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(first + i), value, 0u);
+    if (r != CUDA_SUCCESS) throw Error("cuStreamWriteValue32 failed with code " + std::to_string((int)r));
+  }
+}
+
+// Panel flags of the copy-engine feed: one buffer per device that is never cleared.  Every call
+// takes the next number; its flag writes store that number and its kernel waits for a flag to
+// reach it, so neither a memset nor a fresh allocation sits in front of a launch.
+struct CeFlags {
+  at::Tensor words;
+  uint32_t epoch = 0;
+};
+CeFlags& ce_flags(int device, int panels) {
+  static CeFlags all[64];
+  CeFlags& f = all[device & 63];
+  if (!f.words.defined() || f.words.numel() < panels) {
+    f.words = at::zeros({std::max<int64_t>(panels, 1024)}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+    f.epoch = 0;
+  }
+  return f;
+}
+
+// One fused call fed by the copy engines.  Order of enqueueing: the event that holds the copies
+// back until everything queued so far on `compute` is done (earlier readers of w_full), then the
+// GEMM kernel, which starts on the own panels at once, then the copies and flag writes on the
+// copy stream while the kernel already runs; the copies need no SM, so they progress beside the
+// persistent kernel.  `panels_per_copy` <= 0: one copy per peer shard.
+cudaError_t launch_fed_by_copy_engines(GemmArgs& a, char* w_full, int panels_per_copy, cudaStream_t compute, int device) {
   const int P = a.g.size, me = a.g.first_local;
   const int tpr = (a.N / P) / kGemmBN;
   const uint64_t panel_bytes = (uint64_t)kGemmBN * a.K * 2;
   const int ppc = panels_per_copy > 0 ? std::min(panels_per_copy, tpr) : tpr;
   CopyLane& l = copy_lane(device);
-  WriteValue32Fn wv = write_value32();
+  CeFlags& f = ce_flags(device, a.N / kGemmBN);
+  a.gather_ctas = 0;
+  a.panel_flags = reinterpret_cast<uint32_t*>(f.words.data_ptr<int>());
+  a.flag_target = ++f.epoch;
+  if (a.flag_target == 0) a.flag_target = ++f.epoch;     // 0 is what a fresh buffer holds
   PCCL_CUDA(cudaEventRecord(l.ready, compute));
+  const cudaError_t e = launch_gemm_sm100(a, sm_count(device), compute);
+  if (e != cudaSuccess) return e;
   PCCL_CUDA(cudaStreamWaitEvent(l.stream, l.ready, 0));
   for (int k = 1; k < P; ++k) {
     const int p = (me + k) % P;
@@ -238,10 +290,7 @@ void enqueue_copy_engine_gather(const GemmArgs& a, char* w_full, int panels_per_
       const uint64_t dst_off = ((uint64_t)p * tpr + j0) * panel_bytes;
       PCCL_CUDA(cudaMemcpyAsync(w_full + dst_off, a.g.heap[p] + a.shard_off + (uint64_t)j0 * panel_bytes,
                                 (uint64_t)n * panel_bytes, cudaMemcpyDeviceToDevice, l.stream));
-      for (int j = j0; j < j0 + n; ++j) {
-        const CUresult r = wv(reinterpret_cast<CUstream>(l.stream), reinterpret_cast<CUdeviceptr>(a.panel_flags + p * tpr + j), 1u, 0u);
-        if (r != CUDA_SUCCESS) throw Error("cuStreamWriteValue32 failed with code " + std::to_string((int)r));
-      }
+      stream_write_words(l.stream, a.panel_flags + p * tpr + j0, n, a.flag_target);
     }
   }
   // the own rows last: the kernel multiplies them straight out of the shard, the copy only
@@ -249,12 +298,9 @@ void enqueue_copy_engine_gather(const GemmArgs& a, char* w_full, int panels_per_
   const uint64_t own_bytes = (uint64_t)tpr * panel_bytes;
   PCCL_CUDA(cudaMemcpyAsync(w_full + (uint64_t)me * own_bytes, a.g.heap[me] + a.shard_off, own_bytes, cudaMemcpyDeviceToDevice,
                             l.stream));
-}
-
-void finish_copy_engine_gather(cudaStream_t compute, int device) {
-  CopyLane& l = copy_lane(device);
   PCCL_CUDA(cudaEventRecord(l.done, l.stream));
   PCCL_CUDA(cudaStreamWaitEvent(compute, l.done, 0));   // later work on `compute` sees the whole gathered weight
+  return cudaSuccess;
 }
 
 int even_gatherers(int gather_ctas, bool two_cta) {
@@ -298,16 +344,12 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm(Comm& c, int gid, const at::Tensor& A
     PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
     return {C, err};
   }
-  at::Tensor flags = at::zeros({N / kGemmBN}, A.options().dtype(at::kInt));
-  a.panel_flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
   c.begin_call(gid, &a.g, stream);
   if (copy_engine) {
-    a.gather_ctas = 0;
-    a.flag_target = 1;
-    enqueue_copy_engine_gather(a, (char*)w_full.data_ptr(), panels_per_copy, stream, dev);
-    PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
-    finish_copy_engine_gather(stream, dev);
+    PCCL_CUDA(launch_fed_by_copy_engines(a, (char*)w_full.data_ptr(), panels_per_copy, stream, dev));
   } else {
+    at::Tensor flags = at::zeros({N / kGemmBN}, A.options().dtype(at::kInt));    // counters: one add per gatherer CTA
+    a.panel_flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
     a.gather_ctas = even_gatherers(gather_ctas, two_cta);
     PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
   }
@@ -347,11 +389,7 @@ std::tuple<at::Tensor, at::Tensor> ag_gemm_local(const at::Tensor& A, std::vecto
   }
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
   if (copy_engine) {
-    a.gather_ctas = 0;
-    a.flag_target = 1;
-    enqueue_copy_engine_gather(a, (char*)w_full.data_ptr(), panels_per_copy, stream, dev);
-    PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));
-    finish_copy_engine_gather(stream, dev);
+    PCCL_CUDA(launch_fed_by_copy_engines(a, (char*)w_full.data_ptr(), panels_per_copy, stream, dev));
   } else {
     a.gather_ctas = even_gatherers(gather_ctas, two_cta);
     PCCL_CUDA(launch_gemm_sm100(a, sm_count(dev), stream));

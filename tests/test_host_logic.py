@@ -398,3 +398,30 @@ def test_last_round_split_covers_every_k_block_once():
     assert C.gemm_sk_tiles(8192, 8192, 2048, sms) == 0 or True     # 1024 tiles on 74 pairs: 13.84 rounds
     assert C.gemm_sk_tiles(8192, 2048, 2048, sms) == G + 256 % G
     assert C.gemm_sk_tiles(2048, 2048, 8192, sms) == 64            # fewer tiles than pairs: all of them are split
+
+
+def test_tuner_takes_the_eager_variant_only_where_it_fits(monkeypatch, tmp_path):
+    """`eager` needs the world group's eager area: P x bytes for an all-gather, (P-1) x bytes per block
+    for a reduce-scatter.  Where it does not fit, or on another group (capacity 0), the next
+    preference is taken."""
+    import json
+
+    table = {"all_gather": {"8": [[1 << 20, ["eager", "direct"], 32], [None, ["direct"], 64]]},
+             "reduce_scatter": {"8": [[1 << 20, ["eager", "pull", "direct"], 32], [None, ["pull", "direct"], 64]]}}
+    path = tmp_path / "t.json"
+    path.write_text(json.dumps(table))
+    monkeypatch.setattr(tuner, "TABLE_PATH", path)
+    tuner.reload_table()
+    try:
+        cap = 8 << 20
+        assert tuner.choose("all_gather", 8, 1 << 20, eager_capacity=cap)[0] == sch.EAGER        # 8 x 1 MiB fits exactly
+        assert tuner.choose("all_gather", 8, (1 << 20) + 16, eager_capacity=cap)[0] == sch.DIRECT
+        assert tuner.choose("all_gather", 8, 1 << 10, eager_capacity=0)[0] == sch.DIRECT         # not the world group
+        assert tuner.choose("reduce_scatter", 8, 1 << 20, eager_capacity=cap, symmetric_in=True)[0] == sch.EAGER
+        assert tuner.choose("reduce_scatter", 8, 1 << 20, eager_capacity=1 << 20, symmetric_in=True)[0] == sch.PULL
+        assert tuner.choose("reduce_scatter", 8, 1 << 20, eager_capacity=1 << 20, symmetric_in=False)[0] == sch.DIRECT
+        # an explicit request that does not fit degrades to direct instead of failing
+        assert tuner.choose("all_gather", 8, 64 << 20, requested=sch.EAGER, eager_capacity=cap)[0] == sch.DIRECT
+    finally:
+        monkeypatch.undo()
+        tuner.reload_table()
