@@ -72,6 +72,8 @@ def parse_args():
                     help="weight-gradient GEMMs on a second stream beside the memory-bound backward kernels")
     ap.add_argument("--fused-gelu-gemm", type=int, default=int(os.environ.get("PCCL_FUSED_GELU_GEMM", "0")),
                     help="FC1 on the library's tcgen05 GEMM with bias+GELU in the epilogue")
+    ap.add_argument("--fused-gelu-bwd", type=int, default=int(os.environ.get("PCCL_FUSED_GELU_BWD", "1")),
+                    help="GELU backward as the epilogue of the data-gradient GEMM in front of it (library GEMM only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-baseline", action="store_true", help="library arm only: skip the NCCL+cuBLAS arm and vs_baseline")
     ap.add_argument("--no-raw", action="store_true", help="skip the raw-collective rows")
@@ -149,7 +151,7 @@ def run_arm(args, impl: str, ctx: dict) -> dict:
     engine = Zero3Engine(cfg, TorchBackend(), OptimConfig(), device=dev, comm=comm, micro_batch=mb,
                          fused_ag_gemm=(library and bool(args.fused_ag_gemm)), gather_ctas=args.gather_ctas,
                          fused_gelu_gemm=(library and bool(args.fused_gelu_gemm)), overlap_wgrad=bool(args.overlap_wgrad),
-                         native_gemm=(library and args.gemm == "pccl"),
+                         native_gemm=(library and args.gemm == "pccl"), fused_gelu_bwd_gemm=bool(args.fused_gelu_bwd),
                          copy_engine_gather=(library and args.gather == "copy_engine"))
     host_tokens, dev_tokens = ctx["host_tokens"], ctx["dev_tokens"]
 
@@ -191,6 +193,7 @@ def run_arm(args, impl: str, ctx: dict) -> dict:
         "gpu_launches": launches,
         "engine": {"fused_ag_gemm": bool(engine.fused_ag_gemm), "fused_gelu_gemm": bool(engine.fused_gelu_gemm),
                    "overlap_wgrad": bool(engine.overlap_wgrad), "native_gemm": bool(engine.native_gemm),
+                   "fused_gelu_bwd_gemm": bool(engine.fused_gelu_bwd_gemm),
                    "copy_engine_gather": bool(engine.copy_engine_gather)},
     }
     if not args.no_e2e:
@@ -314,7 +317,7 @@ def main() -> None:
                 "gemm": "tcgen05 (this repository)" if main_arm["engine"]["native_gemm"] else "cuBLAS",
                 "parameter_gather": "copy engines" if main_arm["engine"]["copy_engine_gather"] else
                                     ("all-gather kernels" if args.impl == "pccl" and world > 1 else "nccl" if world > 1 else "none (one rank)"),
-                **{k: v for k, v in main_arm["engine"].items() if k in ("fused_ag_gemm", "fused_gelu_gemm", "overlap_wgrad")},
+                **{k: v for k, v in main_arm["engine"].items() if k in ("fused_ag_gemm", "fused_gelu_gemm", "fused_gelu_bwd_gemm", "overlap_wgrad")},
                 "l2": "working set per step (tens of GB) exceeds the 126 MB L2; no explicit flush",
                 "transport": comm.transport_name if (comm is not None and args.impl == "pccl") else "nccl",
             },

@@ -35,6 +35,9 @@ struct GemmArgs {
   void* C;              // [M,N] bf16 row-major, N % 8 == 0
   const void* bias;     // [N] bf16 or nullptr
   void* act_out;        // [M,N] bf16 or nullptr: second output, gelu(C) in the tanh form (C keeps the pre-activation)
+  const void* gelu_grad_of;  // [M,N] bf16 or nullptr (CTA-pair form): every result is multiplied by gelu'(u) of the
+                        // element of this tensor at its place before it is rounded: with A = dy, W = the second
+                        // MLP weight and u = the first layer's pre-activation this is the whole GELU backward
   int* error;           // device int, set non-zero when a bounded wait ran out
   int two_cta;          // use the 2-SM MMA form (cta_group::2, one 256x256 tile per CTA pair); fused mode
                         // then needs an even gather_ctas (gatherers are whole pairs)

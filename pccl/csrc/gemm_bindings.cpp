@@ -128,7 +128,7 @@ std::tuple<at::Tensor, at::Tensor> gemm(const at::Tensor& A, const at::Tensor& W
 // so (false,false) is a linear layer's forward, (false,true) its data gradient dy * W and
 // (true,true) its weight gradient dy^T * x.  bias (length N) is optional.
 at::Tensor gemm_ex(const at::Tensor& A, const at::Tensor& B, bool a_mn, bool b_mn, std::optional<at::Tensor> bias,
-                   std::optional<at::Tensor> out) {
+                   std::optional<at::Tensor> out, std::optional<at::Tensor> gelu_grad_of) {
   check_bf16_2d(A, "A");
   check_bf16_2d(B, "B");
   const int M = (int)(a_mn ? A.size(1) : A.size(0)), K = (int)(a_mn ? A.size(0) : A.size(1));
@@ -149,6 +149,12 @@ at::Tensor gemm_ex(const at::Tensor& A, const at::Tensor& B, bool a_mn, bool b_m
   a.two_cta = 1;
   a.a_mn = a_mn ? 1 : 0;
   a.b_mn = b_mn ? 1 : 0;
+  if (gelu_grad_of.has_value()) {
+    check_bf16_2d(*gelu_grad_of, "gelu_grad_of");
+    TORCH_CHECK(gelu_grad_of->size(0) == M && gelu_grad_of->size(1) == N && !bias.has_value(),
+                "gelu_grad_of must have the shape of the result, and excludes a bias");
+    a.gelu_grad_of = gelu_grad_of->data_ptr();
+  }
   cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
   maybe_split_last_wave(a, A.get_device(), stream);
   PCCL_CUDA(launch_gemm_sm100(a, sm_count(A.get_device()), stream));
@@ -404,8 +410,9 @@ void bind_gemm(py::module_& m) {
         py::arg("two_cta") = true,
         "C = A @ W^T (+bias) on the tcgen05 tensor cores; returns (C, error_flag)");
   m.def("gemm_ex", &gemm_ex, py::arg("A"), py::arg("B"), py::arg("a_mn") = false, py::arg("b_mn") = false,
-        py::arg("bias") = py::none(), py::arg("out") = py::none(),
-        "C = opA * opB on the CTA-pair tcgen05 kernel; a_mn: A stored [K,M]; b_mn: B stored [K,N] (else [N,K])");
+        py::arg("bias") = py::none(), py::arg("out") = py::none(), py::arg("gelu_grad_of") = py::none(),
+        "C = opA * opB on the CTA-pair tcgen05 kernel; a_mn: A stored [K,M]; b_mn: B stored [K,N] (else [N,K]); "
+        "gelu_grad_of: C is multiplied elementwise by gelu'(u) of this [M,N] tensor in the epilogue");
   m.def("gemm_set_split_last_wave", [](bool on) { g_split_last_wave = on; }, py::arg("on"),
         "split the tiles of a partly filled last round along K over all CTA pairs (default on)");
   m.def("gemm_set_tuning", [](int max_pairs, int group_m) { g_max_pairs = max_pairs; g_group_m = group_m; },

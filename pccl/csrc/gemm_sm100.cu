@@ -928,6 +928,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         }
         __syncwarp();
+        if (a.gelu_grad_of != nullptr && row0 + lane < a.M) {
+          // result *= gelu'(u[row, col]): this thread's 64 columns of u are 128 contiguous bytes
+          const __nv_bfloat16* urow = reinterpret_cast<const __nv_bfloat16*>(a.gelu_grad_of) + (size_t)(row0 + lane) * a.N + col0;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            if (col0 + c * 8 < a.N) {
+              const uint4 uq = __ldg(reinterpret_cast<const uint4*>(urow + c * 8));
+              const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float u0 = __uint_as_float(uw[e] << 16), u1 = __uint_as_float(uw[e] & 0xffff0000u);
+                r[c * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[c * 8 + 2 * e]) * gelu_tanh_grad(u0));
+                r[c * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[c * 8 + 2 * e + 1]) * gelu_tanh_grad(u1));
+              }
+            }
+          }
+        }
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -1074,6 +1091,8 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a_in, int sm_count, cudaStream_t s
   if (a.gather_ctas > 0 && !fused) return cudaErrorInvalidValue;
   if (fused && a.gather_ctas == 0 && !a.two_cta) return cudaErrorInvalidValue;   // externally filled panels: CTA-pair form only
   if ((a.a_mn || a.b_mn) && (!a.two_cta || fused)) return cudaErrorInvalidValue;   // layouts: plain CTA-pair form only
+  if (a.gelu_grad_of != nullptr && (!a.two_cta || a.bias != nullptr || (reinterpret_cast<uintptr_t>(a.gelu_grad_of) & 15u)))
+    return cudaErrorInvalidValue;
   if (a.a_mn && (a.M % 64) != 0) return cudaErrorInvalidValue;
   if (a.b_mn && (a.N % 64) != 0) return cudaErrorInvalidValue;
   const void* own = a.W;

@@ -202,6 +202,7 @@ _native = None
 native_launches = 0     # kernels of this library launched by the functions below
 native_gemm = True       # dense products on the library's tcgen05 GEMM (off: cuBLAS through torch; set by the engine)
 fused_gelu_gemm = False  # FC1 on the tcgen05 GEMM with the GELU in its epilogue (set by the engine)
+fused_gelu_bwd_gemm = True   # the GELU backward as the epilogue of the data-gradient GEMM in front of it (with native_gemm)
 
 
 def _kernels():
@@ -336,6 +337,7 @@ def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[s
     run beside the memory-bound kernels of the chain (GELU backward, layer-norm backward, the
     q/k/v packing) instead of between them.  The current stream waits for ``side`` before the
     function returns, and every tensor a side-stream GEMM reads stays referenced until then."""
+    global native_launches
     x, mean1, rstd1, h1, qd, kd, vd, att, a, x2, mean2, rstd2, h2, u, g = ctx
     T, d = x.shape
     S, H, dh = T // batch, cfg.n_head, cfg.head_dim
@@ -354,8 +356,15 @@ def layer_backward(dy: torch.Tensor, ctx, p: Dict[str, torch.Tensor], gr: Dict[s
     else:
         _bias_grad(dy, gr["fc2_b"])
     wgrad(dy, g, gr["fc2_w"])
-    dg = mm_nn(dy, p["fc2_w"])
-    du = _gelu_bwd(dg, u, gr["fc1_b"])
+    if fused_gelu_bwd_gemm and _gemm_ok(dy, p["fc2_w"], u) and u.shape[1] % 64 == 0 and dy.shape[1] % 8 == 0:
+        # du = (dy @ fc2_w) * gelu'(u) in one kernel: the product never exists in memory; the bias
+        # gradient of FC1 is the column sum of du
+        native_launches += 1
+        du = _kernels().gemm_ex(dy, p["fc2_w"], False, True, None, None, u)
+        _bias_grad(du, gr["fc1_b"])
+    else:
+        dg = mm_nn(dy, p["fc2_w"])
+        du = _gelu_bwd(dg, u, gr["fc1_b"])
     wgrad(du, h2, gr["fc1_w"])
     dh2 = mm_nn(du, p["fc1_w"])
     # dx2 is the gradient of the attention projection's output: its column sums are proj_b's gradient

@@ -351,6 +351,7 @@ def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm, over
     # per block: 2 ln_fwd, GELU (its own kernel, or none when it rides in FC1's epilogue), gelu_bwd, cat3,
     # 2 x (ln_bwd + finalize), and the twelve dense products (4 forward, 4 data gradients, 4 weight
     # gradients); head: ln_fwd, ln_bwd + finalize and its three dense products
+    # (the GELU backward rides in the data-gradient GEMM of FC2 and leaves a column sum behind: same count)
     per_block = 8 + (0 if fused_gelu_gemm else 1) + 12
     expected = cfg.n_layer * per_block + 3 + 3
     if overlap_wgrad:

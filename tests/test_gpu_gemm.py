@@ -219,3 +219,21 @@ def test_last_round_split_along_k(shape, layout):
             assert float((g.float() - ref_g).abs().max()) <= 1e-2 * float(ref_g.abs().max()) + 1e-3
     finally:
         C.gemm_set_split_last_wave(True)
+
+
+@pytest.mark.parametrize("shape", [(512, 768, 256), (960, 512, 328), (8192, 8192, 2048), (1024, 2048, 4096)])
+def test_gemm_with_gelu_backward_epilogue(shape):
+    """du = (dy @ W) * gelu'(u): the GELU backward as the epilogue of the data-gradient product (W stored
+    [K, N], read as it lies), with and without tiles that are split along K."""
+    import pccl
+
+    M, N, K = shape
+    dy, W = rnd((M, K), 1), rnd((K, N), 2, 0.05)
+    u = rnd((M, N), 3, 1.5)
+    du = pccl._C.gemm_ex(dy, W, False, True, None, None, u)
+    torch.cuda.synchronize()
+    assert int(pccl._C.gemm_error_word(0).item()) == 0
+    uf = u.float().requires_grad_()
+    torch.nn.functional.gelu(uf, approximate="tanh").sum().backward()
+    ref = (dy.float() @ W.float()) * uf.grad
+    check_close(du, ref, K)
