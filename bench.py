@@ -61,7 +61,8 @@ def parse_args():
     ap.add_argument("--algorithm", default="auto")
     ap.add_argument("--lanes", type=int, default=int(os.environ.get("PCCL_TRAIN_LANES", "16")),
                     help="SMs a gradient reduction (or a kernel-driven parameter gather) may occupy while it overlaps the GEMMs")
-    ap.add_argument("--nvls", type=int, default=int(os.environ.get("PCCL_ENABLE_NVLS", "0")))
+    ap.add_argument("--nvls", type=int, default=int(os.environ.get("PCCL_ENABLE_NVLS", "1")),
+                    help="bind an NVLS multicast mapping where the machine offers one (the multimem variants win the small sizes)")
     ap.add_argument("--gemm", default=os.environ.get("PCCL_GEMM", "pccl"), choices=["pccl", "cublas"],
                     help="library arm: dense products on the repository's tcgen05 GEMM (default) or on cuBLAS")
     ap.add_argument("--gather", default=os.environ.get("PCCL_GATHER", "copy_engine"), choices=["copy_engine", "kernel"],
@@ -72,8 +73,10 @@ def parse_args():
                     help="weight-gradient GEMMs on a second stream beside the memory-bound backward kernels")
     ap.add_argument("--fused-gelu-gemm", type=int, default=int(os.environ.get("PCCL_FUSED_GELU_GEMM", "0")),
                     help="FC1 on the library's tcgen05 GEMM with bias+GELU in the epilogue")
-    ap.add_argument("--fused-gelu-bwd", type=int, default=int(os.environ.get("PCCL_FUSED_GELU_BWD", "1")),
+    ap.add_argument("--fused-gelu-bwd", type=int, default=int(os.environ.get("PCCL_FUSED_GELU_BWD", "0")),
                     help="GELU backward as the epilogue of the data-gradient GEMM in front of it (library GEMM only)")
+    ap.add_argument("--dynamic-tiles", type=int, default=int(os.environ.get("PCCL_DYNAMIC_TILES", "-1")),
+                    help="library GEMM hands tiles out at run time: 1 on, 0 off, -1 on when N > 1")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-baseline", action="store_true", help="library arm only: skip the NCCL+cuBLAS arm and vs_baseline")
     ap.add_argument("--no-raw", action="store_true", help="skip the raw-collective rows")
@@ -152,6 +155,7 @@ def run_arm(args, impl: str, ctx: dict) -> dict:
                          fused_ag_gemm=(library and bool(args.fused_ag_gemm)), gather_ctas=args.gather_ctas,
                          fused_gelu_gemm=(library and bool(args.fused_gelu_gemm)), overlap_wgrad=bool(args.overlap_wgrad),
                          native_gemm=(library and args.gemm == "pccl"), fused_gelu_bwd_gemm=bool(args.fused_gelu_bwd),
+                         dynamic_tiles=None if args.dynamic_tiles < 0 else bool(args.dynamic_tiles),
                          copy_engine_gather=(library and args.gather == "copy_engine"))
     host_tokens, dev_tokens = ctx["host_tokens"], ctx["dev_tokens"]
 
@@ -193,7 +197,7 @@ def run_arm(args, impl: str, ctx: dict) -> dict:
         "gpu_launches": launches,
         "engine": {"fused_ag_gemm": bool(engine.fused_ag_gemm), "fused_gelu_gemm": bool(engine.fused_gelu_gemm),
                    "overlap_wgrad": bool(engine.overlap_wgrad), "native_gemm": bool(engine.native_gemm),
-                   "fused_gelu_bwd_gemm": bool(engine.fused_gelu_bwd_gemm),
+                   "fused_gelu_bwd_gemm": bool(engine.fused_gelu_bwd_gemm), "dynamic_tiles": bool(engine.dynamic_tiles),
                    "copy_engine_gather": bool(engine.copy_engine_gather)},
     }
     if not args.no_e2e:
@@ -317,7 +321,7 @@ def main() -> None:
                 "gemm": "tcgen05 (this repository)" if main_arm["engine"]["native_gemm"] else "cuBLAS",
                 "parameter_gather": "copy engines" if main_arm["engine"]["copy_engine_gather"] else
                                     ("all-gather kernels" if args.impl == "pccl" and world > 1 else "nccl" if world > 1 else "none (one rank)"),
-                **{k: v for k, v in main_arm["engine"].items() if k in ("fused_ag_gemm", "fused_gelu_gemm", "fused_gelu_bwd_gemm", "overlap_wgrad")},
+                **{k: v for k, v in main_arm["engine"].items() if k in ("fused_ag_gemm", "fused_gelu_gemm", "fused_gelu_bwd_gemm", "overlap_wgrad", "dynamic_tiles")},
                 "l2": "working set per step (tens of GB) exceeds the 126 MB L2; no explicit flush",
                 "transport": comm.transport_name if (comm is not None and args.impl == "pccl") else "nccl",
             },

@@ -106,25 +106,22 @@ def tuning_rows(points: List[Dict]) -> List[List]:
     ``points``: dictionaries with ``per_rank_bytes``, the tuner's key (all-gather: bytes each rank
     contributes; reduce-scatter: bytes of the per-rank INPUT BUFFER, converted here to the result
     block the tuner is asked about) and ``variants`` = {name: {"ms": ...}}.  For every size the
-    preference list is: the fastest variant, then the fastest one that needs no multicast mapping,
-    then ``direct`` (which every tensor placement can run).  Neighbouring sizes with the same list
-    share a row; a row covers sizes up to and including its ``max_bytes``, the last one everything
-    above."""
+    preference list is every measured variant, fastest first (the tuner takes the first one the
+    tensors' placement allows, so a private input or a missing multicast mapping falls to the next
+    best instead of to a fixed default), with ``direct``, which every placement can run, at the
+    latest as the last entry.  Neighbouring sizes whose first three preferences agree share a row; a
+    row covers sizes up to and including its ``max_bytes``, the last one everything above."""
     pts = sorted(points, key=lambda p: p["per_rank_bytes"])
     rows: List[List] = []
     for p in pts:
-        order = sorted(p["variants"], key=lambda a: p["variants"][a]["ms"])
-        prefs = [order[0]]
-        plain = [a for a in order if a != "multimem"]
-        if plain and plain[0] not in prefs:
-            prefs.append(plain[0])
+        prefs = sorted(p["variants"], key=lambda a: p["variants"][a]["ms"])
         if "direct" not in prefs:
             prefs.append("direct")
         key_bytes = p["per_rank_bytes"]
         if p["collective"] == "reduce_scatter":
             key_bytes //= p["P"]
         lanes = 32 if key_bytes <= (4 << 20) else 64
-        if rows and rows[-1][1] == prefs and rows[-1][2] == lanes:
+        if rows and rows[-1][1][:3] == prefs[:3] and rows[-1][2] == lanes:
             rows[-1][0] = key_bytes
         else:
             rows.append([key_bytes, prefs, lanes])

@@ -66,6 +66,15 @@ struct GemmArgs {
   float* sk_scratch;    // per pair 2 x 128 x 256 floats (256 KiB)
   uint32_t* sk_flags;   // per pair 8 words (one per epilogue warp of the pair), holding the last epoch written
   uint32_t sk_epoch;    // differs from launch to launch on the same scratch
+  // ---- tiles handed out at run time (CTA-pair form; sched_counter == nullptr: static round-robin)
+  // A persistent kernel that deals its tiles out in advance assumes that all its CTA pairs start
+  // together.  Beside a collective kernel that holds a few SMs (a gradient reduction overlapping the
+  // backward pass) some pairs start late and would then work through their whole share alone.  With
+  // a counter, every pair takes the next tile when it is ready for one: late pairs simply take fewer.
+  // The counter is never reset: a launch's tiles are counter values sched_base .. sched_base+tiles-1,
+  // and the host advances its base by tiles + pairs per launch (every pair draws one value too many).
+  uint32_t* sched_counter;   // device word, shared by the launches of one stream
+  uint32_t sched_base;
   // ---- tuning knobs (0: the default)
   int max_pairs;        // use at most this many CTA pairs (plain mode)
   int group_m;          // row-tiles per band of the tile walk (plain mode; default 8); negative: bands of

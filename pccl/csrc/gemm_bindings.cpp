@@ -48,8 +48,11 @@ at::Tensor& error_word(int device) {
 struct SkWorkspace {
   at::Tensor scratch, flags;
   uint32_t epoch = 0;
+  at::Tensor counter;          // tiles handed out at run time: the draw counter of this stream
+  uint32_t next_base = 0;
 };
 bool g_split_last_wave = true;
+bool g_dynamic_tiles = false;  // hand tiles out at run time instead of dealing them out in advance
 int g_max_pairs = 0, g_group_m = 0;      // tuning knobs, 0: the kernel's defaults
 
 SkWorkspace& sk_workspace(int device, cudaStream_t stream, int pairs) {
@@ -62,6 +65,8 @@ SkWorkspace& sk_workspace(int device, cudaStream_t stream, int pairs) {
     w.scratch = at::empty({floats}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device));
     w.flags = at::zeros({(int64_t)pairs * (int64_t)kGemmSkFlagsPerPair}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
     w.epoch = 0;
+    w.counter = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+    w.next_base = 0;
   }
   return w;
 }
@@ -71,6 +76,18 @@ void maybe_split_last_wave(GemmArgs& a, int device, cudaStream_t stream) {
   a.max_pairs = g_max_pairs;
   a.group_m = g_group_m;
   if (g_max_pairs > 0) return;           // a reduced grid is for measurements of the plain walk
+  if (g_dynamic_tiles && a.two_cta) {
+    // every pair draws its next tile from a counter; the counter runs on from launch to launch
+    const int sms = sm_count(device);
+    int pairs = (sms - a.gather_ctas) / 2;
+    const int tiles = ((a.M + 255) / 256) * ((a.N + 255) / 256);
+    if (a.panel_flags == nullptr && tiles < pairs) pairs = tiles;
+    SkWorkspace& w = sk_workspace(device, stream, sms / 2);
+    a.sched_counter = reinterpret_cast<uint32_t*>(w.counter.data_ptr<int>());
+    a.sched_base = w.next_base;
+    w.next_base += (uint32_t)tiles + (uint32_t)pairs;
+    return;
+  }
   if (!g_split_last_wave || !a.two_cta || a.panel_flags != nullptr) return;
   const int sms = sm_count(device);
   const int n = gemm_sk_tiles(a.M, a.N, a.K, sms);
@@ -413,6 +430,9 @@ void bind_gemm(py::module_& m) {
         py::arg("bias") = py::none(), py::arg("out") = py::none(), py::arg("gelu_grad_of") = py::none(),
         "C = opA * opB on the CTA-pair tcgen05 kernel; a_mn: A stored [K,M]; b_mn: B stored [K,N] (else [N,K]); "
         "gelu_grad_of: C is multiplied elementwise by gelu'(u) of this [M,N] tensor in the epilogue");
+  m.def("gemm_set_dynamic_tiles", [](bool on) { g_dynamic_tiles = on; }, py::arg("on"),
+        "CTA pairs draw their tiles from a counter at run time (robust beside kernels that hold some SMs) instead of a "
+        "fixed round-robin share; excludes the split of the last round");
   m.def("gemm_set_split_last_wave", [](bool on) { g_split_last_wave = on; }, py::arg("on"),
         "split the tiles of a partly filled last round along K over all CTA pairs (default on)");
   m.def("gemm_set_tuning", [](int max_pairs, int group_m) { g_max_pairs = max_pairs; g_group_m = group_m; },

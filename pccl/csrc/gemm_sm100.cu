@@ -599,6 +599,67 @@ __device__ __forceinline__ uint4 pack8(const uint32_t* r, const float* b, uint4*
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// ---- tiles drawn at run time.  The producer thread of the leader CTA draws the next tile number
+// from the global counter and hands it to every other role of the pair (the peer CTA's producer,
+// the MMA issuer, the eight epilogue warps) through a four-slot ring in each CTA's shared memory:
+// value written into both CTAs, then one arrival on each CTA's `ready` barrier of the slot; a
+// reader copies the value and arrives on the leader's `taken` barrier at once, so a slot is free
+// again as soon as all ten readers have looked at it.
+constexpr int kSchedSlots = 4;
+constexpr uint32_t kSchedReaders = 10;     // peer producer, MMA issuer, 2 x 4 epilogue warps
+constexpr int kSchedDone = -1;
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool sched_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t it = 0;
+  for (;;) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++it & 255u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > kWaitNs) return false;
+    }
+  }
+}
+struct SchedRing {
+  int* tile;            // kSchedSlots values
+  uint64_t* ready;      // kSchedSlots barriers, one arrival (the scheduler's)
+  uint64_t* taken;      // kSchedSlots barriers in the LEADER CTA, kSchedReaders arrivals
+};
+// Scheduler (leader CTA's producer thread): draw, publish to both CTAs.  Returns false on a wait that ran out.
+__device__ __forceinline__ bool sched_draw(const GemmArgs& a, const SchedRing& r, uint32_t n, int total, volatile int* abort_flag, int* t) {
+  const uint32_t slot = n % kSchedSlots, ph = (n / kSchedSlots) & 1u;
+  if (!sched_wait(r.taken + slot, ph ^ 1u, abort_flag)) return false;
+  const uint32_t v = atomicAdd(a.sched_counter, 1u) - a.sched_base;
+  const int tile = v < (uint32_t)total ? (int)v : kSchedDone;
+  r.tile[slot] = tile;
+  const uint32_t peer_tile = map_to_cta(smem_u32(r.tile + slot), 1);
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(peer_tile), "r"(tile) : "memory");
+  mbar_arrive_cluster(map_to_cta(smem_u32(r.ready + slot), 0));
+  mbar_arrive_cluster(map_to_cta(smem_u32(r.ready + slot), 1));
+  *t = tile;
+  return true;
+}
+// Reader (one thread): wait for slot n, copy the value, give the slot back.
+__device__ __forceinline__ bool sched_read(const SchedRing& r, uint32_t n, volatile int* abort_flag, int* t) {
+  const uint32_t slot = n % kSchedSlots, ph = (n / kSchedSlots) & 1u;
+  if (!sched_wait(r.ready + slot, ph, abort_flag)) return false;
+  *t = *reinterpret_cast<volatile int*>(r.tile + slot);
+  mbar_arrive_cluster(map_to_cta(smem_u32(r.taken + slot), 0));
+  return true;
+}
+
 // The work of one CTA pair as a sequence of items (tile, first k-block, end k-block): first its
 // run of the k-block sequence of the leading sk_tiles tiles (see GemmArgs), then whole tiles
 // sk_tiles + pair, + npairs, ...  Producer, MMA issuer and epilogue walk the same sequence.
@@ -658,6 +719,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  SchedRing ring;
+  ring.ready = reinterpret_cast<uint64_t*>(tmem_slot + 2);
+  ring.taken = ring.ready + kSchedSlots;
+  ring.tile = reinterpret_cast<int*>(ring.taken + kSchedSlots);
+  const bool dynamic = a.sched_counter != nullptr;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages2; ++s) {
@@ -667,6 +733,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     for (int i = 0; i < 2; ++i) {
       mbar_init(tmem_full + i, 1);
       mbar_init(tmem_empty + i, 8);        // four epilogue warps of each CTA
+    }
+    for (int i = 0; i < kSchedSlots; ++i) {
+      mbar_init(ring.ready + i, 1);
+      mbar_init(ring.taken + i, kSchedReaders);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -722,7 +792,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     bool ok = true;
     WorkIter work(pair, npairs, total, nkb, a.sk_tiles);
     int t, kb0, kb1;
-    while (ok && work.next(&t, &kb0, &kb1)) {
+    uint32_t drawn = 0;
+    auto next_item = [&]() -> bool {
+      if (!dynamic) return work.next(&t, &kb0, &kb1);
+      kb0 = 0;
+      kb1 = nkb;
+      const bool got = leader ? sched_draw(a, ring, drawn, total, abort_flag, &t) : sched_read(ring, drawn, abort_flag, &t);
+      ++drawn;
+      if (!got) {
+        ok = false;
+        atomicCAS(a.error, 0, kErrProducer);
+        return false;
+      }
+      return t != kSchedDone;
+    };
+    while (ok && next_item()) {
       int m_idx, n_idx;
       decode(t, &m_idx, &n_idx);
       const CUtensorMap* wmap = &tmW;
@@ -782,7 +866,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     bool ok = true;
     WorkIter work(pair, npairs, total, nkb, a.sk_tiles);
     int t, kb0, kb1;
-    for (; ok && work.next(&t, &kb0, &kb1); ++tile_count) {
+    auto next_item = [&]() -> bool {
+      if (!dynamic) return work.next(&t, &kb0, &kb1);
+      kb0 = 0;
+      kb1 = nkb;
+      if (!sched_read(ring, tile_count, abort_flag, &t)) {
+        ok = false;
+        return false;
+      }
+      return t != kSchedDone;
+    };
+    for (; ok && next_item(); ++tile_count) {
       const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
       if (!gemm_wait(tmem_empty + acc, acc_ph ^ 1u, abort_flag)) {
         ok = false;
@@ -833,7 +927,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const size_t sk_warp = ((size_t)rank * 4 + (size_t)q) * (32 * 256);
     const uint32_t sk_word = rank * 4 + (uint32_t)q;
     int t, kb0, kb1;
-    for (; ok && work.next(&t, &kb0, &kb1); ++tile_count) {
+    auto next_item = [&]() -> bool {
+      if (!dynamic) return work.next(&t, &kb0, &kb1);
+      kb0 = 0;
+      kb1 = nkb;
+      int got = 1;
+      if (lane == 0) got = sched_read(ring, tile_count, abort_flag, &t) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      t = __shfl_sync(0xffffffffu, t, 0);
+      if (!got) {
+        ok = false;
+        return false;
+      }
+      return t != kSchedDone;
+    };
+    for (; ok && next_item(); ++tile_count) {
       int m_idx, n_idx;
       decode(t, &m_idx, &n_idx);
       const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
@@ -1127,6 +1235,7 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a_in, int sm_count, cudaStream_t s
     } else if (!fused && tiles2 < pairs) {
       pairs = tiles2;
     }
+    if (a.sched_counter != nullptr && a.sk_tiles > 0) return cudaErrorInvalidValue;   // one way of dealing out tiles at a time
     if (!fused && a.max_pairs > 0 && a.max_pairs < pairs) pairs = a.max_pairs;
     if (pairs < 1) return cudaErrorInvalidValue;
     const int grid = a.gather_ctas + pairs * 2;

@@ -202,7 +202,7 @@ _native = None
 native_launches = 0     # kernels of this library launched by the functions below
 native_gemm = True       # dense products on the library's tcgen05 GEMM (off: cuBLAS through torch; set by the engine)
 fused_gelu_gemm = False  # FC1 on the tcgen05 GEMM with the GELU in its epilogue (set by the engine)
-fused_gelu_bwd_gemm = True   # the GELU backward as the epilogue of the data-gradient GEMM in front of it (with native_gemm)
+fused_gelu_bwd_gemm = False  # the GELU backward as the epilogue of the data-gradient GEMM in front of it (with native_gemm)
 
 
 def _kernels():

@@ -96,7 +96,8 @@ class Zero3Engine:
                  device: Optional[torch.device] = None, seed: int = 1234, comm=None, group=None,
                  linear_fwd: Optional[Callable] = None, micro_batch: int = 1, fused_ag_gemm: bool = False,
                  gather_ctas: int = 16, fused_gelu_gemm: bool = False, overlap_wgrad: bool = False,
-                 native_gemm: bool = True, copy_engine_gather: bool = False, fused_gelu_bwd_gemm: bool = True):
+                 native_gemm: bool = True, copy_engine_gather: bool = False, fused_gelu_bwd_gemm: bool = False,
+                 dynamic_tiles: Optional[bool] = None):
         from .. import build_kernels
 
         self.C = build_kernels.load()
@@ -112,6 +113,10 @@ class Zero3Engine:
         # every dense product of the model on the library's tcgen05 GEMM (False: cuBLAS through torch,
         # which is what the baseline arm measures)
         self.native_gemm = bool(native_gemm)
+        # The library GEMM hands its tiles out at run time instead of dealing them out in advance.  Default:
+        # on when other ranks exist, because then gradient reductions hold some SMs while the backward GEMMs
+        # run, and CTA pairs that start late would otherwise work through a full share alone.
+        self.dynamic_tiles = (self.world > 1) if dynamic_tiles is None else bool(dynamic_tiles)
         # GELU backward as the epilogue of the data-gradient GEMM of FC2 (needs native_gemm)
         self.fused_gelu_bwd_gemm = bool(fused_gelu_bwd_gemm) and self.native_gemm
         # parameter gathers by the GPU's copy engines instead of gather kernels (no SM is taken from
@@ -316,6 +321,7 @@ class Zero3Engine:
         branch = None          # MLP output of the previous block; the next layer norm adds it to x in its own pass
         gpt.fused_gelu_gemm = self.fused_gelu_gemm
         gpt.native_gemm = self.native_gemm
+        C.gemm_set_dynamic_tiles(self.dynamic_tiles)
         gpt.fused_gelu_bwd_gemm = self.fused_gelu_bwd_gemm
         saved = []
         for li in range(1, L + 1):

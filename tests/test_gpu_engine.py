@@ -324,8 +324,9 @@ def test_gelu_forward_and_backward_with_bias_gradient(shape):
         torch.testing.assert_close(gb.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()) + 1e-3)
 
 
-@pytest.mark.parametrize("fused_gelu_gemm,overlap_wgrad", [(False, False), (True, False), (False, True)])
-def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm, overlap_wgrad):
+@pytest.mark.parametrize("fused_gelu_gemm,overlap_wgrad,gelu_bwd_gemm",
+                         [(False, False, False), (True, False, False), (False, True, False), (False, False, True)])
+def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm, overlap_wgrad, gelu_bwd_gemm):
     """A two-block model wide enough (d = 1024) for the fused add+layer-norm, layer-norm backward
     with residual, GELU and GELU-backward kernels, with FC1 optionally on the tcgen05 GEMM whose
     epilogue applies the GELU: loss and every gradient against torch autograd in fp32."""
@@ -338,7 +339,7 @@ def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm, over
     init_distributed()
     cfg = GPTConfig(2, 1024, 8, 4096, vocab=2048, seq_len=128, name="gpt-test-1024")
     engine = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=0.0, weight_decay=0.0), fused_gelu_gemm=fused_gelu_gemm,
-                         overlap_wgrad=overlap_wgrad)
+                         overlap_wgrad=overlap_wgrad, fused_gelu_bwd_gemm=gelu_bwd_gemm)
     g = torch.Generator().manual_seed(11)
     toks = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=g).to(DEV)
     tokens, targets = toks[:, :-1].contiguous(), toks[:, 1:].contiguous()
@@ -351,7 +352,8 @@ def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm, over
     # per block: 2 ln_fwd, GELU (its own kernel, or none when it rides in FC1's epilogue), gelu_bwd, cat3,
     # 2 x (ln_bwd + finalize), and the twelve dense products (4 forward, 4 data gradients, 4 weight
     # gradients); head: ln_fwd, ln_bwd + finalize and its three dense products
-    # (the GELU backward rides in the data-gradient GEMM of FC2 and leaves a column sum behind: same count)
+    # (with gelu_bwd_gemm the GELU backward rides in the data-gradient GEMM of FC2 and leaves a column sum
+    # behind: same count)
     per_block = 8 + (0 if fused_gelu_gemm else 1) + 12
     expected = cfg.n_layer * per_block + 3 + 3
     if overlap_wgrad:

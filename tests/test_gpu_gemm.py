@@ -237,3 +237,35 @@ def test_gemm_with_gelu_backward_epilogue(shape):
     torch.nn.functional.gelu(uf, approximate="tanh").sum().backward()
     ref = (dy.float() @ W.float()) * uf.grad
     check_close(du, ref, K)
+
+
+@pytest.mark.parametrize("shape,layout", [((8192, 2048, 2048), "nt"), ((1000, 520, 328), "nt"), ((4096, 2048, 8192), "nn"),
+                                          ((2048, 2048, 4096), "tn"), ((256, 256, 64), "nt"), ((8192, 6144, 2048), "nt")])
+def test_tiles_drawn_at_run_time(shape, layout):
+    """The other way of dealing out tiles: every CTA pair draws its next tile from a counter that runs on
+    from launch to launch.  Repeated launches, with bias, same results as the fixed shares."""
+    import pccl
+
+    C = pccl._C
+    M, N, K = shape
+    a, w = rnd((M, K), 1), rnd((N, K), 2, 0.05)
+    bias = rnd((N,), 3)
+    ref = a.float() @ w.float().t()
+    if layout == "nt":
+        run = lambda: C.gemm_ex(a, w, False, False, bias, None)  # noqa: E731
+        ref = ref + bias.float()
+    elif layout == "nn":
+        wt = w.t().contiguous()
+        run = lambda: C.gemm_ex(a, wt, False, True, None, None)  # noqa: E731
+    else:
+        at_, wt = a.t().contiguous(), w.t().contiguous()
+        run = lambda: C.gemm_ex(at_, wt, True, True, None, None)  # noqa: E731
+    try:
+        C.gemm_set_dynamic_tiles(True)
+        for _ in range(4):
+            y = run()
+            torch.cuda.synchronize()
+            assert int(C.gemm_error_word(0).item()) == 0
+            check_close(y, ref, K)
+    finally:
+        C.gemm_set_dynamic_tiles(False)
