@@ -153,7 +153,7 @@ def test_engine_step_matches_autograd():
     patch_deepspeed(1)
     try:
         cfg = PRESETS["gpt-tiny"]
-        engine = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=0.0, weight_decay=0.0), comm=comm)
+        engine = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=0.0, weight_decay=0.0), comm=comm, native_gemm=True)
         assert engine.symmetric and engine.local_only
         g = torch.Generator().manual_seed(3)
         toks = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=g).to(DEV)
@@ -170,7 +170,7 @@ def test_engine_step_matches_autograd():
                 assert err < 6e-2, f"unit {u.name} grad {name}: relative error {float(err):.3e}"
         assert engine.launches > 0
         # training moves the loss
-        engine2 = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=1e-3), comm=comm)
+        engine2 = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=1e-3), comm=comm, native_gemm=True)
         losses = [float(engine2.train_step(tokens, targets)) for _ in range(5)]
         assert losses[-1] < losses[0]
         # pinned-host inputs take the same path
@@ -200,7 +200,7 @@ def test_engine_same_loss_over_torch_backend():
     comm = pccl.init(heap_bytes=256 << 20, staging_bytes=32 << 20)
     patch_deepspeed(1)
     try:
-        ours = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=1e-3), comm=comm)
+        ours = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=1e-3), comm=comm, native_gemm=True)
         l_ours = [float(ours.train_step(toks[:, :-1], toks[:, 1:])) for _ in range(3)]
     finally:
         unpatch_deepspeed()
@@ -339,7 +339,7 @@ def test_engine_fused_kernels_match_autograd_at_width_1024(fused_gelu_gemm, over
     init_distributed()
     cfg = GPTConfig(2, 1024, 8, 4096, vocab=2048, seq_len=128, name="gpt-test-1024")
     engine = Zero3Engine(cfg, TorchBackend(), OptimConfig(lr=0.0, weight_decay=0.0), fused_gelu_gemm=fused_gelu_gemm,
-                         overlap_wgrad=overlap_wgrad, fused_gelu_bwd_gemm=gelu_bwd_gemm)
+                         overlap_wgrad=overlap_wgrad, fused_gelu_bwd_gemm=gelu_bwd_gemm, native_gemm=True)
     g = torch.Generator().manual_seed(11)
     toks = torch.randint(0, cfg.vocab, (2, cfg.seq_len + 1), generator=g).to(DEV)
     tokens, targets = toks[:, :-1].contiguous(), toks[:, 1:].contiguous()
