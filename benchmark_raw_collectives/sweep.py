@@ -59,7 +59,8 @@ def main() -> None:
     ap.add_argument("--rs-sizes", default=None, help="per-rank input buffer sizes (default 8M..8G)")
     ap.add_argument("--algorithms", default="all", help="comma list or 'all'")
     ap.add_argument("--nvls", type=int, default=1)
-    ap.add_argument("--lanes", type=int, default=None)
+    ap.add_argument("--lanes", default=None,
+                    help="lanes (CTAs) per call; a comma list times every variant at every count (rows named variant@lanes)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--test", action="store_true", help="check every variant against NCCL at every size")
@@ -108,6 +109,9 @@ def main() -> None:
             v.append(sch.MULTIMEM)
         return v
 
+    lane_counts = [int(x) for x in str(args.lanes).split(",") if x] if args.lanes else [None]
+    if len(lane_counts) > 1 and args.write_tuning_table:
+        raise SystemExit("--write-tuning-table needs one lane count (or none), not a list")
     rows: List[Dict] = []
     ok_all = True
     for sweep, collective, dtype, nbytes in plan:
@@ -122,8 +126,8 @@ def main() -> None:
             def nccl():
                 dist.all_gather_into_tensor(gold if gold is not None else out, inp)
 
-            def ours(a):
-                return lambda: pccl._all_gather(out, inp, group, use_pccl_cpp_backend=True, algorithm=a, lanes=args.lanes)
+            def ours(a, lanes=None):
+                return lambda: pccl._all_gather(out, inp, group, use_pccl_cpp_backend=True, algorithm=a, lanes=lanes)
 
             wire = nbytes                                   # bytes every rank contributes
         else:
@@ -138,9 +142,9 @@ def main() -> None:
             def nccl():
                 dist.reduce_scatter_tensor(gold, inp)
 
-            def ours(a):
+            def ours(a, lanes=None):
                 return lambda: pccl._reduce_scatter(out, inp, group, use_pccl_cpp_backend=True, algorithm=a,
-                                                    lanes=args.lanes)
+                                                    lanes=lanes)
 
             wire = n * es                                   # bytes of one block
         ms_nccl = time_something(nccl, warmup_iters=args.warmup, timed_iters=args.iters)
@@ -152,8 +156,11 @@ def main() -> None:
         cap = comm.native.eager_capacity
         if args.algorithms == "all" and cap > 0 and (world * nbytes if collective == "all_gather" else (world - 1) * wire) <= cap:
             names = names + [sch.EAGER]
+        if len(lane_counts) > 1:
+            names = [f"{a}@{n_l}" for a in names for n_l in lane_counts]
         for a in names:
-            fn = ours(a)
+            algo, _, at = a.partition("@")
+            fn = ours(algo, int(at) if at else lane_counts[0])
             ms = time_something(fn, warmup_iters=args.warmup, timed_iters=args.iters)
             comm.check()
             good = None
@@ -175,7 +182,7 @@ def main() -> None:
                 ok_all = ok_all and good
             rec["variants"][a] = {"ms": round(ms, 5), "busbw_gbs": round(busbw(ms), 2),
                                   "vs_nccl": round(ms_nccl / ms, 3) if ms > 0 else None, "correct": good}
-        plain = {a: v for a, v in rec["variants"].items() if a != sch.MULTIMEM}
+        plain = {a: v for a, v in rec["variants"].items() if a.partition("@")[0] != sch.MULTIMEM}
         for key, pool in (("best", rec["variants"]), ("best_without_multimem", plain)):
             if pool:
                 a = min(pool, key=lambda k: pool[k]["ms"])
