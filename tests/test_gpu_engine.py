@@ -223,7 +223,7 @@ def test_col_sum_matches_fp32_reference(shape):
         torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=1e-2 * float(ref.abs().max()))
 
 
-@pytest.mark.parametrize("shape", [(8192, 2048), (333, 1024), (4096, 4096), (1, 2048)])
+@pytest.mark.parametrize("shape", [(8192, 2048), (333, 1024), (4096, 4096), (1, 2048), (1237, 2048)])
 def test_layer_norm_backward_matches_fp32_reference(shape):
     import pccl
 
