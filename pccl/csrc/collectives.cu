@@ -43,9 +43,13 @@ __device__ __forceinline__ bool lane_copy(BulkPipe& pipe, char* const* dsts, int
     done = len & ~(uint64_t)15;
     if (!cta_bulk_copy(pipe, dsts, ndst, src, done)) return false;
   }
-  if (done < len)
+  if (done < len) {
+    char* rest[kMaxRanks + 1];
+    int nr = 0;
     for (int d = 0; d < ndst; ++d)
-      if (dsts[d] + done != src + done) cta_copy<REMOTE_SRC>(dsts[d] + done, src + done, len - done);
+      if (dsts[d] != src) rest[nr++] = dsts[d] + done;
+    cta_copy_multi<REMOTE_SRC>(rest, nr, src + done, len - done);
+  }
   return true;
 }
 template <bool REMOTE_SRC>

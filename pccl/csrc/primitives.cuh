@@ -71,7 +71,8 @@ __device__ __forceinline__ void report_failure(const GroupDev& g, int li, uint32
 }
 
 // One thread spins until flag >= epoch (wrap-safe), the time limit runs out, or the
-// communicator is poisoned.  Never traps, never spins without a limit.
+// communicator is poisoned.  Never traps, never spins without a limit.  (Polling with relaxed
+// loads and one acquire fence at the end was tried and was not faster.)
 __device__ __forceinline__ bool spin_until(const uint32_t* flag, uint32_t epoch, const GroupDev& g, int li,
                                            uint32_t* seen_out) {
   uint32_t v = ld_acquire_sys(flag);
@@ -260,6 +261,53 @@ __device__ __forceinline__ void cta_copy(char* __restrict__ dst, const char* __r
   }
 }
 
+// The same range to several destinations in one pass: every vector is loaded once and stored
+// ndst times (a pass per destination pays the load latency ndst times, which is most of the
+// time of a small all-gather to seven peers).  Falls back to a pass per destination when the
+// pointers do not share their alignment within 16 bytes.
+template <bool REMOTE_SRC>
+__device__ __forceinline__ void cta_copy_multi(char* const* dsts, int ndst, const char* __restrict__ src, uint64_t n) {
+  if (n == 0 || ndst == 0) return;
+  const uintptr_t ss = reinterpret_cast<uintptr_t>(src);
+  bool congruent = true;
+  for (int d = 0; d < ndst; ++d) congruent = congruent && ((reinterpret_cast<uintptr_t>(dsts[d]) ^ ss) & 15u) == 0;
+  if (ndst == 1 || !congruent) {
+    for (int d = 0; d < ndst; ++d) cta_copy<REMOTE_SRC>(dsts[d], src, n);
+    return;
+  }
+  const uint64_t tid = threadIdx.x, nt = blockDim.x;
+  uint64_t head = (16 - (ss & 15u)) & 15u;
+  if (head > n) head = n;
+  for (uint64_t i = tid; i < head; i += nt) {
+    const char b = src[i];
+    for (int d = 0; d < ndst; ++d) dsts[d][i] = b;
+  }
+  const uint64_t nvec = (n - head) >> 4;
+  const char* s = src + head;
+  constexpr int U = 4;
+  uint64_t i = tid;
+  for (; i + (U - 1) * nt < nvec; i += U * nt) {
+    uint4 v[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k)
+      v[k] = REMOTE_SRC ? ld_volatile_v4(s + ((i + k * nt) << 4)) : ld_v4(s + ((i + k * nt) << 4));
+    for (int d = 0; d < ndst; ++d) {
+      char* o = dsts[d] + head;
+#pragma unroll
+      for (int k = 0; k < U; ++k) st_v4(o + ((i + k * nt) << 4), v[k]);
+    }
+  }
+  for (; i < nvec; i += nt) {
+    const uint4 v = REMOTE_SRC ? ld_volatile_v4(s + (i << 4)) : ld_v4(s + (i << 4));
+    for (int d = 0; d < ndst; ++d) st_v4(dsts[d] + head + (i << 4), v);
+  }
+  const uint64_t done = head + (nvec << 4);
+  for (uint64_t j = done + tid; j < n; j += nt) {
+    const char b = src[j];
+    for (int d = 0; d < ndst; ++d) dsts[d][j] = b;
+  }
+}
+
 // ---------------------------------------------------------------- typed 8-element vectors
 template <int DT>
 struct Elem;
@@ -365,6 +413,76 @@ __device__ __forceinline__ void store8_all(char* const* outs, int nout, uint64_t
 
 // outs: nout destinations that all receive the same result (nout > 1: the broadcast half
 // of an all-reduce).
+// 8 elements of type DT as they sit in memory (one 16-byte vector, two for fp32), and their sum into acc.
+template <int DT>
+struct Raw8 {
+  uint4 v[Elem<DT>::size == 4 ? 2 : 1];
+};
+template <int DT, bool REMOTE>
+__device__ __forceinline__ void load8_raw(const char* p, Raw8<DT>& r) {
+  r.v[0] = REMOTE ? ld_volatile_v4(p) : ld_v4(p);
+  if constexpr (DT == kF32) r.v[1] = REMOTE ? ld_volatile_v4(p + 16) : ld_v4(p + 16);
+}
+template <int DT>
+__device__ __forceinline__ void add8_raw(const Raw8<DT>& r, float* acc) {
+  if constexpr (DT == kF32) {
+    acc[0] += __uint_as_float(r.v[0].x); acc[1] += __uint_as_float(r.v[0].y);
+    acc[2] += __uint_as_float(r.v[0].z); acc[3] += __uint_as_float(r.v[0].w);
+    acc[4] += __uint_as_float(r.v[1].x); acc[5] += __uint_as_float(r.v[1].y);
+    acc[6] += __uint_as_float(r.v[1].z); acc[7] += __uint_as_float(r.v[1].w);
+  } else {
+    float t[8];
+    Elem<DT>::unpack(r.v[0], t);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += t[e];
+  }
+}
+
+// The vector part of cta_reduce: G groups of 8 elements per thread and iteration, every load of
+// up to KW sources at a time issued before the first add.  With a loop over the sources that adds as it
+// loads, the (volatile) loads of peer memory run one round trip after another: seven peers cost
+// seven NVLink latencies per iteration.  Sums are formed in source order, as before.
+template <int TA, int TW, int TOUT, bool REMOTE_W, int G, int KW>
+__device__ __forceinline__ uint64_t cta_reduce_groups(char* const* outs, int nout, const char* a, const char* const* w,
+                                                      int nw, uint64_t i, uint64_t ngroups, float scale) {
+  constexpr uint64_t SA = 8 * Elem<TA>::size, SW = 8 * Elem<TW>::size, SO = 8 * Elem<TOUT>::size;
+  const uint64_t nt = blockDim.x;
+  for (; i + (G - 1) * nt < ngroups; i += G * nt) {
+    float acc[G][8];
+    Raw8<TW> raw[G][KW];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (a != nullptr) {
+        load8<TA, false>(a + (i + g * nt) * SA, acc[g]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+      }
+    }
+    for (int k0 = 0; k0 < nw; k0 += KW) {            // one pass unless there are more than KW sources
+#pragma unroll
+      for (int k = 0; k < KW; ++k)
+        if (k0 + k < nw) {
+#pragma unroll
+          for (int g = 0; g < G; ++g) load8_raw<TW, REMOTE_W>(w[k0 + k] + (i + g * nt) * SW, raw[g][k]);
+        }
+#pragma unroll
+      for (int k = 0; k < KW; ++k)
+        if (k0 + k < nw) {
+#pragma unroll
+          for (int g = 0; g < G; ++g) add8_raw<TW>(raw[g][k], acc[g]);
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] *= scale;
+      store8_all<TOUT>(outs, nout, (i + g * nt) * SO, acc[g]);
+    }
+  }
+  return i;
+}
+
 template <int TA, int TW, int TOUT, bool REMOTE_W>
 __device__ __forceinline__ void cta_reduce(char* const* outs, int nout, const char* a,
                                            const char* const* w, int nw, uint64_t count, float scale) {
@@ -376,52 +494,11 @@ __device__ __forceinline__ void cta_reduce(char* const* outs, int nout, const ch
   uint64_t done = 0;
   if (aligned) {
     const uint64_t ngroups = count >> 3;
-    constexpr uint64_t SA = 8 * Elem<TA>::size, SW = 8 * Elem<TW>::size, SO = 8 * Elem<TOUT>::size;
     uint64_t i = tid;
-    // two groups in flight per thread
-    for (; i + nt < ngroups; i += 2 * nt) {
-      float acc0[8], acc1[8], t0[8], t1[8];
-      if (a != nullptr) {
-        load8<TA, false>(a + i * SA, acc0);
-        load8<TA, false>(a + (i + nt) * SA, acc1);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc0[e] = acc1[e] = 0.f;
-      }
-      for (int k = 0; k < nw; ++k) {
-        load8<TW, REMOTE_W>(w[k] + i * SW, t0);
-        load8<TW, REMOTE_W>(w[k] + (i + nt) * SW, t1);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          acc0[e] += t0[e];
-          acc1[e] += t1[e];
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        acc0[e] *= scale;
-        acc1[e] *= scale;
-      }
-      store8_all<TOUT>(outs, nout, i * SO, acc0);
-      store8_all<TOUT>(outs, nout, (i + nt) * SO, acc1);
-    }
-    for (; i < ngroups; i += nt) {
-      float acc[8], t[8];
-      if (a != nullptr) {
-        load8<TA, false>(a + i * SA, acc);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      }
-      for (int k = 0; k < nw; ++k) {
-        load8<TW, REMOTE_W>(w[k] + i * SW, t);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += t[e];
-      }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] *= scale;
-      store8_all<TOUT>(outs, nout, i * SO, acc);
-    }
+    // at most 32 registers of source vectors in flight per thread
+    constexpr int kWide = Elem<TW>::size == 4 ? 2 : 1;      // 16-byte vectors per 8 elements
+    if (nw <= 1) i = cta_reduce_groups<TA, TW, TOUT, REMOTE_W, 2, 1>(outs, nout, a, w, nw, i, ngroups, scale);
+    i = cta_reduce_groups<TA, TW, TOUT, REMOTE_W, 1, 4 / kWide>(outs, nout, a, w, nw, i, ngroups, scale);
     done = ngroups << 3;
   }
   for (uint64_t i = done + tid; i < count; i += nt) {

@@ -23,7 +23,7 @@ from . import schedule as sch
 TABLE_PATH = Path(__file__).resolve().parent / "tuning_table.json"
 
 # Fallback when the table has no row: bytes each lane should at least move, lane ceiling.
-MIN_BYTES_PER_LANE = 128 << 10
+MIN_BYTES_PER_LANE = 64 << 10
 DEFAULT_MAX_LANES = 148
 
 
