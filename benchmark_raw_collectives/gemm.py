@@ -144,11 +144,15 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--step-shapes", action="store_true",
                     help="time every dense product of a GPT-1.3B training step (all three layouts) against cuBLAS")
+    ap.add_argument("--wide", type=int, default=-1,
+                    help="plain CTA-pair products in units of two row-tiles that share their W half: 1 always, 0 never, "
+                         "-1 where it was measured faster (gemm_set_wide)")
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     rank, world, _ = init_distributed()
     dev = torch.device("cuda", torch.cuda.current_device())
     import pccl
+    pccl._C.gemm_set_wide(args.wide)
     from pccl.ops.ag_gemm import AllGatherLinear, auto_gather_ctas
 
     peaks = {}

@@ -79,6 +79,10 @@ struct GemmArgs {
   int max_pairs;        // use at most this many CTA pairs (plain mode)
   int group_m;          // row-tiles per band of the tile walk (plain mode; default 8); negative: bands of
                         // -group_m column-tiles walked along M instead
+  // Plain CTA-pair products only: work in units of two vertically adjacent 256 x 256 tiles that share
+  // their W half in shared memory (three quarters of the operand bytes per FLOP from L2; both TMEM
+  // accumulators belong to one unit).  Ignored with sk_tiles, sched_counter, panel flags or M <= 256.
+  int wide;
 };
 
 // Bytes of sk_scratch / words of sk_flags needed for `pairs` CTA pairs.

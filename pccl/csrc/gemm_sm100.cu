@@ -697,7 +697,12 @@ struct WorkIter {
 // The pair whose run of the split sequence (I k-blocks over G pairs) holds k-block i.
 __device__ __forceinline__ int sk_pair_of(long long i, long long I, int G) { return (int)(((i + 1) * G + I - 1) / I) - 1; }
 
-template <bool A_MN, bool B_MN>
+// WIDE: the unit of work is two vertically adjacent 256 x 256 tiles that share their W half:
+// a stage holds two A halves and one W half (48 KiB, four stages), the MMA issuer feeds both
+// accumulators of TMEM from it, and the epilogue drains them as two ordinary tiles.  A quarter
+// fewer operand bytes come from L2 per FLOP; the price is that both accumulators belong to one
+// unit, so the epilogue of a unit overlaps only the first k-blocks of the next.
+template <bool A_MN, bool B_MN, bool WIDE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     gemm_sm100_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                            const __grid_constant__ CUtensorMap tmWown, const __grid_constant__ CUtensorMap tmC,
@@ -752,7 +757,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_m = (a.M + 255) / 256, tiles_n = (a.N + 255) / 256;
+  constexpr int NST = WIDE ? 4 : kStages2;                                  // stages in flight
+  constexpr uint32_t SB = WIDE ? 3 * kHalfBytes : kStage2Bytes;             // bytes of one stage in one CTA
+  constexpr uint32_t W_OFF = WIDE ? 2 * kHalfBytes : kHalfBytes;            // where the W half sits in a stage
+  const int tiles_m = WIDE ? (a.M + 511) / 512 : (a.M + 255) / 256, tiles_n = (a.N + 255) / 256;   // WIDE: units of two row-tiles
   const int total = tiles_m * tiles_n;
   const bool fused = a.panel_flags != nullptr;       // W arrives panel by panel
   // Tiles are walked in bands: `group` row-tiles deep and all column-tiles wide (or, transposed,
@@ -839,21 +847,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           asm volatile("fence.proxy.async;" ::: "memory");
         }
       }
-      const int ay = m_idx * 256 + (int)rank * 128;
+      const int ay = m_idx * (WIDE ? 512 : 256) + (int)rank * 128;
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const uint32_t s = it % kStages2, ph = (it / kStages2) & 1u;
+        const uint32_t s = it % NST, ph = (it / NST) & 1u;
         if (!gemm_wait(empty + s, ph ^ 1u, abort_flag)) {
           ok = false;
           atomicCAS(a.error, 0, kErrProducer);
           break;
         }
-        unsigned char* sa = smem + (size_t)s * kStage2Bytes;
-        if (leader) mbar_expect_tx(full + s, 2 * kStage2Bytes);     // both CTAs' bytes land on this barrier
+        unsigned char* sa = smem + (size_t)s * SB;
+        if (leader) mbar_expect_tx(full + s, 2 * SB);                // both CTAs' bytes land on this barrier
         const uint32_t bar = map_to_cta(smem_u32(full + s), 0);      // the leader's barrier, from either CTA
         if (A_MN) tma_load_3d_pair(sa, &tmA, 0, kb * BK, ay >> 6, bar);
         else tma_load_2d_pair(sa, &tmA, kb * BK, ay, bar);
-        if (B_MN) tma_load_3d_pair(sa + kHalfBytes, wmap, 0, kb * BK, wy >> 6, bar);
-        else tma_load_2d_pair(sa + kHalfBytes, wmap, kb * BK, wy, bar);
+        if (WIDE) {
+          // the lower row-tile of the unit (rows past M read zeros)
+          if (A_MN) tma_load_3d_pair(sa + kHalfBytes, &tmA, 0, kb * BK, (ay + 256) >> 6, bar);
+          else tma_load_2d_pair(sa + kHalfBytes, &tmA, kb * BK, ay + 256, bar);
+        }
+        if (B_MN) tma_load_3d_pair(sa + W_OFF, wmap, 0, kb * BK, wy >> 6, bar);
+        else tma_load_2d_pair(sa + W_OFF, wmap, kb * BK, wy, bar);
       }
     }
     if (!ok) *abort_flag = 1;
@@ -876,27 +889,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       }
       return t != kSchedDone;
     };
-    for (; ok && next_item(); ++tile_count) {
+    for (; ok && next_item(); tile_count += WIDE ? 2 : 1) {
+      // WIDE: a unit fills both accumulators, so tile_count stays even and acc is 0
       const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
-      if (!gemm_wait(tmem_empty + acc, acc_ph ^ 1u, abort_flag)) {
+      if (!gemm_wait(tmem_empty + acc, acc_ph ^ 1u, abort_flag) ||
+          (WIDE && !gemm_wait(tmem_empty + 1, acc_ph ^ 1u, abort_flag))) {
         ok = false;
         break;
       }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const uint32_t s = it % kStages2, ph = (it / kStages2) & 1u;
+        const uint32_t s = it % NST, ph = (it / NST) & 1u;
         if (!gemm_wait(full + s, ph, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + (size_t)s * kStage2Bytes);
+        const uint32_t sa = smem_u32(smem + (size_t)s * SB);
         const uint64_t da = A_MN ? smem_desc_mn(sa) : smem_desc(sa);
-        const uint64_t db = B_MN ? smem_desc_mn(sa + kHalfBytes) : smem_desc(sa + kHalfBytes);
+        const uint64_t db = B_MN ? smem_desc_mn(sa + W_OFF) : smem_desc(sa + W_OFF);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)
           mma_bf16_pair(d_tmem, da + (uint64_t)k * a_step, db + (uint64_t)k * b_step, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        if (WIDE) {
+          const uint64_t da1 = A_MN ? smem_desc_mn(sa + kHalfBytes) : smem_desc(sa + kHalfBytes);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            mma_bf16_pair(d_tmem + BN, da1 + (uint64_t)k * a_step, db + (uint64_t)k * b_step, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        }
         const uint32_t eb = smem_u32(empty + s);
         mma_commit_pair(map_to_cta(eb, 0));     // free the stage in both CTAs
         mma_commit_pair(map_to_cta(eb, 1));
@@ -905,6 +926,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       const uint32_t fb = smem_u32(tmem_full + acc);
       mma_commit_pair(map_to_cta(fb, 0));       // accumulator complete: wake both epilogues
       mma_commit_pair(map_to_cta(fb, 1));
+      if (WIDE) {
+        const uint32_t fb1 = smem_u32(tmem_full + 1);
+        mma_commit_pair(map_to_cta(fb1, 0));
+        mma_commit_pair(map_to_cta(fb1, 1));
+      }
     }
     if (!ok) {
       atomicCAS(a.error, 0, kErrMma);
@@ -941,9 +967,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       }
       return t != kSchedDone;
     };
-    for (; ok && next_item(); ++tile_count) {
+    int sub = 1;                                // WIDE: which row-tile of the current unit comes next
+    auto next_tile = [&]() -> bool {
+      if (!WIDE) return next_item();
+      if (sub == 0) {
+        sub = 1;
+        return true;                            // the lower row-tile of the unit already drawn
+      }
+      if (!next_item()) return false;
+      sub = 0;
+      return true;
+    };
+    for (; ok && next_tile(); ++tile_count) {
       int m_idx, n_idx;
       decode(t, &m_idx, &n_idx);
+      if (WIDE) m_idx = 2 * m_idx + sub;
       const uint32_t acc = tile_count & 1u, acc_ph = (tile_count >> 1) & 1u;
       // one lane polls the barrier (with a pause between polls: an accumulator takes microseconds),
       // the others wait at the shuffle: 124 fewer threads hammering shared memory beside the MMAs
@@ -1157,7 +1195,7 @@ bool make_map_store(CUtensorMap* map, void* base, uint64_t M, uint64_t N) {
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool WIDE = false>
 cudaError_t launch_pair(const CUtensorMap& mA, const CUtensorMap& mW, const CUtensorMap& mOwn, const CUtensorMap& mC,
                         const CUtensorMap& mAct, const GemmArgs& a, int grid, cudaStream_t stream) {
   // the shared-memory limit is an attribute of the function on the current device
@@ -1166,11 +1204,11 @@ cudaError_t launch_pair(const CUtensorMap& mA, const CUtensorMap& mW, const CUte
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    e = cudaFuncSetAttribute(gemm_sm100_2cta_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemm2Smem);
+    e = cudaFuncSetAttribute(gemm_sm100_2cta_kernel<A_MN, B_MN, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemm2Smem);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  gemm_sm100_2cta_kernel<A_MN, B_MN><<<grid, kGemmThreads, kGemm2Smem, stream>>>(mA, mW, mOwn, mC, mAct, a);
+  gemm_sm100_2cta_kernel<A_MN, B_MN, WIDE><<<grid, kGemmThreads, kGemm2Smem, stream>>>(mA, mW, mOwn, mC, mAct, a);
   return cudaGetLastError();
 }
 
@@ -1227,7 +1265,9 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a_in, int sm_count, cudaStream_t s
     } else {
       mAct = mC;
     }
-    const int tiles2 = ((a.M + 255) / 256) * ((a.N + 255) / 256);
+    // units of two row-tiles that share their W half: plain products only, tiles dealt out in advance
+    const bool wide = a.wide != 0 && !fused && a.sk_tiles == 0 && a.sched_counter == nullptr && a.M > 256;
+    const int tiles2 = (wide ? (a.M + 511) / 512 : (a.M + 255) / 256) * ((a.N + 255) / 256);
     int pairs = (sm_count - a.gather_ctas) / 2;
     if (a.sk_tiles > 0) {
       // tiles split along K: every pair takes part, and the partial sums need their scratch
@@ -1239,6 +1279,12 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a_in, int sm_count, cudaStream_t s
     if (!fused && a.max_pairs > 0 && a.max_pairs < pairs) pairs = a.max_pairs;
     if (pairs < 1) return cudaErrorInvalidValue;
     const int grid = a.gather_ctas + pairs * 2;
+    if (wide) {
+      if (a.a_mn && a.b_mn) return launch_pair<true, true, true>(mA, mW, mOwn, mC, mAct, a, grid, stream);
+      if (a.a_mn) return launch_pair<true, false, true>(mA, mW, mOwn, mC, mAct, a, grid, stream);
+      if (a.b_mn) return launch_pair<false, true, true>(mA, mW, mOwn, mC, mAct, a, grid, stream);
+      return launch_pair<false, false, true>(mA, mW, mOwn, mC, mAct, a, grid, stream);
+    }
     if (a.a_mn && a.b_mn) return launch_pair<true, true>(mA, mW, mOwn, mC, mAct, a, grid, stream);
     if (a.a_mn) return launch_pair<true, false>(mA, mW, mOwn, mC, mAct, a, grid, stream);
     if (a.b_mn) return launch_pair<false, true>(mA, mW, mOwn, mC, mAct, a, grid, stream);

@@ -201,6 +201,7 @@ def test_last_round_split_along_k(shape, layout):
         at_, wt = a.t().contiguous(), w.t().contiguous()
         run = lambda: C.gemm_ex(at_, wt, True, True, None, None)  # noqa: E731
     try:
+        C.gemm_set_wide(0)                       # single tiles: the form that splits
         C.gemm_set_split_last_wave(False)
         y_plain = run()
         C.gemm_set_split_last_wave(True)
@@ -219,6 +220,7 @@ def test_last_round_split_along_k(shape, layout):
             assert float((g.float() - ref_g).abs().max()) <= 1e-2 * float(ref_g.abs().max()) + 1e-3
     finally:
         C.gemm_set_split_last_wave(True)
+        C.gemm_set_wide(-1)
 
 
 @pytest.mark.parametrize("shape", [(512, 768, 256), (960, 512, 328), (8192, 8192, 2048), (1024, 2048, 4096)])
@@ -269,3 +271,43 @@ def test_tiles_drawn_at_run_time(shape, layout):
             check_close(y, ref, K)
     finally:
         C.gemm_set_dynamic_tiles(False)
+
+
+@pytest.mark.parametrize("shape,layout", [((8192, 6144, 2048), "nt"), ((300, 256, 64), "nt"), ((1000, 520, 328), "nt"),
+                                          ((12576, 2048, 512), "nt"), ((4096, 2048, 8192), "nn"), ((1280, 512, 320), "tn"),
+                                          ((2048, 2048, 8192), "tn")])
+def test_units_of_two_row_tiles_sharing_w(shape, layout):
+    """The wide form of the CTA-pair kernel: two vertically adjacent 256 x 256 tiles share their W half in
+    shared memory and fill both TMEM accumulators.  Same result as the plain form, bit for bit (the same
+    products are summed in the same order), for full units, a unit whose lower tile is partly or wholly
+    past M, with bias, in all three layouts."""
+    import pccl
+
+    C = pccl._C
+    M, N, K = shape
+    a, w = rnd((M, K), 1), rnd((N, K), 2, 0.05)
+    bias = rnd((N,), 3)
+    ref = a.float() @ w.float().t()
+    if layout == "nt":
+        run = lambda: C.gemm_ex(a, w, False, False, bias, None)  # noqa: E731
+        ref = ref + bias.float()
+    elif layout == "nn":
+        wt = w.t().contiguous()
+        run = lambda: C.gemm_ex(a, wt, False, True, None, None)  # noqa: E731
+    else:
+        at_, wt = a.t().contiguous(), w.t().contiguous()
+        run = lambda: C.gemm_ex(at_, wt, True, True, None, None)  # noqa: E731
+    C.gemm_set_split_last_wave(False)
+    try:
+        C.gemm_set_wide(0)
+        plain = run()
+        C.gemm_set_wide(1)
+        for _ in range(3):
+            y = run()
+            torch.cuda.synchronize()
+            assert int(C.gemm_error_word(0).item()) == 0
+            check_close(y, ref, K)
+            assert torch.equal(y, plain)
+    finally:
+        C.gemm_set_wide(-1)
+        C.gemm_set_split_last_wave(True)
