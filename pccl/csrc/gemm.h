@@ -81,7 +81,7 @@ struct GemmArgs {
                         // -group_m column-tiles walked along M instead
   // Plain CTA-pair products only: work in units of two vertically adjacent 256 x 256 tiles that share
   // their W half in shared memory (three quarters of the operand bytes per FLOP from L2; both TMEM
-  // accumulators belong to one unit).  Ignored with sk_tiles, sched_counter, panel flags or M <= 256.
+  // accumulators belong to one unit).  Ignored with sk_tiles, panel flags or M <= 256.
   int wide;
 };
 

@@ -77,24 +77,21 @@ void maybe_split_last_wave(GemmArgs& a, int device, cudaStream_t stream) {
   a.max_pairs = g_max_pairs;
   a.group_m = g_group_m;
   if (g_wide != 0 && g_max_pairs == 0 && a.two_cta && a.panel_flags == nullptr && a.M > 256) {
-    // Units of two row-tiles (dealt out in advance, never split).  Measured on the training shapes: 6-28 %
-    // faster than single tiles for contractions of 4096 and more when the units fill their rounds, slower for
-    // short contractions, where the epilogue of a unit (both accumulators) is no longer hidden.
+    // Units of two row-tiles (never split along K).  Measured on the training shapes: 6-28 % faster than
+    // single tiles for contractions of 4096 and more when the units fill their rounds, slower for short
+    // contractions, where the epilogue of a unit (both accumulators) is no longer hidden.
     const long long units = (long long)((a.M + 511) / 512) * ((a.N + 255) / 256);
     const long long pairs = sm_count(device) / 2;
     const long long rounds = (units + pairs - 1) / pairs;
     const bool fills = units * 5 >= rounds * pairs * 4;                  // at least 0.8 of the slots of its rounds
-    if (g_wide > 0 || (a.K >= 4096 && fills && !g_dynamic_tiles)) {
-      a.wide = 1;
-      return;
-    }
+    if (g_wide > 0 || (a.K >= 4096 && fills)) a.wide = 1;
   }
   if (g_max_pairs > 0) return;           // a reduced grid is for measurements of the plain walk
   if (g_dynamic_tiles && a.two_cta) {
-    // every pair draws its next tile from a counter; the counter runs on from launch to launch
+    // every pair draws its next tile (or unit) from a counter; the counter runs on from launch to launch
     const int sms = sm_count(device);
     int pairs = (sms - a.gather_ctas) / 2;
-    const int tiles = ((a.M + 255) / 256) * ((a.N + 255) / 256);
+    const int tiles = (a.wide ? (a.M + 511) / 512 : (a.M + 255) / 256) * ((a.N + 255) / 256);
     if (a.panel_flags == nullptr && tiles < pairs) pairs = tiles;
     SkWorkspace& w = sk_workspace(device, stream, sms / 2);
     a.sched_counter = reinterpret_cast<uint32_t*>(w.counter.data_ptr<int>());
@@ -102,6 +99,7 @@ void maybe_split_last_wave(GemmArgs& a, int device, cudaStream_t stream) {
     w.next_base += (uint32_t)tiles + (uint32_t)pairs;
     return;
   }
+  if (a.wide) return;
   if (!g_split_last_wave || !a.two_cta || a.panel_flags != nullptr) return;
   const int sms = sm_count(device);
   const int n = gemm_sk_tiles(a.M, a.N, a.K, sms);

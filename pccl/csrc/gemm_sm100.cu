@@ -875,7 +875,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     constexpr uint32_t idesc = kIdesc2 | (A_MN ? (1u << 15) : 0u) | (B_MN ? (1u << 16) : 0u);
     constexpr uint64_t a_step = A_MN ? (2048 >> 4) : (32 >> 4);   // 16 k further: 16 rows of 128 B, or 32 bytes along the row
     constexpr uint64_t b_step = B_MN ? (2048 >> 4) : (32 >> 4);
-    uint32_t it = 0, tile_count = 0;
+    uint32_t it = 0, tile_count = 0, draws = 0;
     bool ok = true;
     WorkIter work(pair, npairs, total, nkb, a.sk_tiles);
     int t, kb0, kb1;
@@ -883,7 +883,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       if (!dynamic) return work.next(&t, &kb0, &kb1);
       kb0 = 0;
       kb1 = nkb;
-      if (!sched_read(ring, tile_count, abort_flag, &t)) {
+      if (!sched_read(ring, draws++, abort_flag, &t)) {      // draws, not tiles: a unit of two tiles is one draw
         ok = false;
         return false;
       }
@@ -947,6 +947,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
     const uint32_t sw = (uint32_t)(lane & 7);   // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8)
     uint32_t nstore = 0;                        // slabs stored so far: picks the piece, across tiles too
+    uint32_t draws = 0;                         // tiles (or units) taken from the run-time scheduler so far
     WorkIter work(pair, npairs, total, nkb, a.sk_tiles);
     const long long sk_I = (long long)a.sk_tiles * nkb;
     // this warp's 32 x 256 fp32 block inside a pair's scratch slot, and its flag word
@@ -958,7 +959,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       kb0 = 0;
       kb1 = nkb;
       int got = 1;
-      if (lane == 0) got = sched_read(ring, tile_count, abort_flag, &t) ? 1 : 0;
+      if (lane == 0) got = sched_read(ring, draws, abort_flag, &t) ? 1 : 0;
+      ++draws;
       got = __shfl_sync(0xffffffffu, got, 0);
       t = __shfl_sync(0xffffffffu, t, 0);
       if (!got) {
@@ -1266,7 +1268,7 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a_in, int sm_count, cudaStream_t s
       mAct = mC;
     }
     // units of two row-tiles that share their W half: plain products only, tiles dealt out in advance
-    const bool wide = a.wide != 0 && !fused && a.sk_tiles == 0 && a.sched_counter == nullptr && a.M > 256;
+    const bool wide = a.wide != 0 && !fused && a.sk_tiles == 0 && a.M > 256;
     const int tiles2 = (wide ? (a.M + 511) / 512 : (a.M + 255) / 256) * ((a.N + 255) / 256);
     int pairs = (sm_count - a.gather_ctas) / 2;
     if (a.sk_tiles > 0) {

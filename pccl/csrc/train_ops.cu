@@ -57,8 +57,10 @@ __device__ __forceinline__ void col_item(const uint4& q, const uint4& uq, __nv_b
     float u[8];
     unpack8(uq, u);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = round_bf16(f[e] * gelu_tanh_grad(u[e]));
-    *reinterpret_cast<uint4*>(DU + off) = pack8(f);
+    for (int e = 0; e < 8; ++e) f[e] *= gelu_tanh_grad(u[e]);
+    const uint4 packed = pack8(f);               // one rounding; the sums below are of the rounded values
+    *reinterpret_cast<uint4*>(DU + off) = packed;
+    unpack8(packed, f);
   }
   if (MODE == kColCat3) *reinterpret_cast<uint4*>(DU + off) = q;
 #pragma unroll

@@ -276,11 +276,12 @@ def test_tiles_drawn_at_run_time(shape, layout):
 @pytest.mark.parametrize("shape,layout", [((8192, 6144, 2048), "nt"), ((300, 256, 64), "nt"), ((1000, 520, 328), "nt"),
                                           ((12576, 2048, 512), "nt"), ((4096, 2048, 8192), "nn"), ((1280, 512, 320), "tn"),
                                           ((2048, 2048, 8192), "tn")])
-def test_units_of_two_row_tiles_sharing_w(shape, layout):
+@pytest.mark.parametrize("dynamic", [False, True], ids=["dealt_out", "drawn_at_run_time"])
+def test_units_of_two_row_tiles_sharing_w(shape, layout, dynamic):
     """The wide form of the CTA-pair kernel: two vertically adjacent 256 x 256 tiles share their W half in
     shared memory and fill both TMEM accumulators.  Same result as the plain form, bit for bit (the same
     products are summed in the same order), for full units, a unit whose lower tile is partly or wholly
-    past M, with bias, in all three layouts."""
+    past M, with bias, in all three layouts, with the units dealt out in advance or drawn from the counter."""
     import pccl
 
     C = pccl._C
@@ -302,6 +303,7 @@ def test_units_of_two_row_tiles_sharing_w(shape, layout):
         C.gemm_set_wide(0)
         plain = run()
         C.gemm_set_wide(1)
+        C.gemm_set_dynamic_tiles(dynamic)
         for _ in range(3):
             y = run()
             torch.cuda.synchronize()
@@ -309,5 +311,6 @@ def test_units_of_two_row_tiles_sharing_w(shape, layout):
             check_close(y, ref, K)
             assert torch.equal(y, plain)
     finally:
+        C.gemm_set_dynamic_tiles(False)
         C.gemm_set_wide(-1)
         C.gemm_set_split_last_wave(True)
