@@ -51,6 +51,33 @@ def cublas_gemm():
     torch.cuda.synchronize()
 
 
+def gemm_proj(cublas: bool = False):
+    """The output projection of an attention block, 8192 x 2048 out of K = 2048: a short contraction whose
+    operands and result (75 MB) stay in L2 between launches, as inside a training step."""
+    M, N, K = 8192, 2048, 2048
+    A = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    W = (torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(4):
+        if cublas:
+            torch.matmul(A, W.t(), out=out)
+        else:
+            pccl._C.gemm_ex(A, W, False, False, None, out)
+    torch.cuda.synchronize()
+
+
+def gemm_wide():
+    """Units of two row-tiles that share their W half: the data gradient 8192 x 2048 out of K = 8192."""
+    M, N, K = 8192, 2048, 8192
+    dy = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    W = (torch.randn(K, N, device=DEV) * 0.02).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    pccl._C.gemm_set_wide(1)
+    for _ in range(3):
+        pccl._C.gemm_ex(dy, W, False, True, None, out)
+    torch.cuda.synchronize()
+
+
 def _emu():
     return pccl.Communicator.emulated_world(8, device=0, heap_bytes=640 << 20, staging_bytes=16 << 20)
 
@@ -216,7 +243,8 @@ def col_sum():
 
 
 CASES = {
-    "gemm": gemm, "cublas_gemm": cublas_gemm, "gemm_nn": gemm_nn, "gemm_tn": gemm_tn, "gemm_split": gemm_split,
+    "gemm": gemm, "cublas_gemm": cublas_gemm, "gemm_proj": gemm_proj, "cublas_gemm_proj": lambda: gemm_proj(True),
+    "gemm_wide": gemm_wide, "gemm_nn": gemm_nn, "gemm_tn": gemm_tn, "gemm_split": gemm_split,
     "all_gather": all_gather, "all_gather_ring": lambda: _ag(sch.RING), "all_gather_recursive": lambda: _ag(sch.RECURSIVE),
     "reduce_scatter": reduce_scatter, "reduce_scatter_ring": lambda: _rs(sch.RING),
     "reduce_scatter_recursive": lambda: _rs(sch.RECURSIVE),
