@@ -52,6 +52,7 @@ struct SkWorkspace {
   uint32_t next_base = 0;
 };
 bool g_split_last_wave = true;
+bool g_split_single_round = false;        // also split shapes with fewer tiles than CTA pairs (slower back to back: measured)
 bool g_dynamic_tiles = false;  // hand tiles out at run time instead of dealing them out in advance
 int g_max_pairs = 0, g_group_m = 0;      // tuning knobs, 0: the kernel's defaults
 int g_wide = -1;                         // units of two row-tiles that share their W half: 1 always, 0 never, -1 where measured faster
@@ -104,6 +105,9 @@ void maybe_split_last_wave(GemmArgs& a, int device, cudaStream_t stream) {
   const int sms = sm_count(device);
   const int n = gemm_sk_tiles(a.M, a.N, a.K, sms);
   if (n <= 0) return;
+  // fewer tiles than CTA pairs: splitting every tile wins a single cold launch, but back to back under the power
+  // cap the unsplit launch is faster (2048 x 2048 x 8192: 65 against 74 us), so it is opt-in
+  if ((long long)((a.M + 255) / 256) * ((a.N + 255) / 256) < sms / 2 && !g_split_single_round) return;
   SkWorkspace& w = sk_workspace(device, stream, sms / 2);
   a.sk_tiles = n;
   a.sk_scratch = w.scratch.data_ptr<float>();
@@ -445,8 +449,10 @@ void bind_gemm(py::module_& m) {
   m.def("gemm_set_dynamic_tiles", [](bool on) { g_dynamic_tiles = on; }, py::arg("on"),
         "CTA pairs draw their tiles from a counter at run time (robust beside kernels that hold some SMs) instead of a "
         "fixed round-robin share; excludes the split of the last round");
-  m.def("gemm_set_split_last_wave", [](bool on) { g_split_last_wave = on; }, py::arg("on"),
-        "split the tiles of a partly filled last round along K over all CTA pairs (default on)");
+  m.def("gemm_set_split_last_wave", [](bool on, bool single_round) { g_split_last_wave = on; g_split_single_round = single_round; },
+        py::arg("on"), py::arg("single_round") = false,
+        "split the tiles of a partly filled last round along K over all CTA pairs (default on); single_round: also "
+        "when the shape has fewer tiles than CTA pairs (default off)");
   m.def("gemm_set_wide", [](int mode) { g_wide = mode; }, py::arg("mode"),
         "Plain CTA-pair products in units of two vertically adjacent 256 x 256 tiles that share their W half (fewer "
         "operand bytes from L2 and HBM per FLOP; dealt out in advance, no split along K): 1 always, 0 never, "

@@ -204,7 +204,7 @@ def test_last_round_split_along_k(shape, layout):
         C.gemm_set_wide(0)                       # single tiles: the form that splits
         C.gemm_set_split_last_wave(False)
         y_plain = run()
-        C.gemm_set_split_last_wave(True)
+        C.gemm_set_split_last_wave(True, True)   # shapes with fewer tiles than CTA pairs too
         for _ in range(3):                       # repeated launches reuse the scratch and its flags
             y_split = run()
             torch.cuda.synchronize()
