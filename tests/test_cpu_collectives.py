@@ -250,3 +250,44 @@ def _fd_channel_and_max(rank, world):
 
 def test_descriptor_channel_and_max_over_ranks(port):
     run_ranks(_fd_channel_and_max, 3, port)
+
+
+def _peer_missing_at_handle_exchange(rank, world):
+    """Rendezvous failure injected on the host: the last rank never sends its memory handles.
+    The others' receive runs into the channel's timeout, and the phase's agreement step turns that
+    into the same PcclError on EVERY rank (the silent one included), so nobody falls out of step
+    or hangs; the ranks can then go on (here: one more collective on the process group)."""
+    import os
+    import tempfile
+    import types
+
+    from pccl.comm import Communicator, PcclError, _FdChannel
+
+    job = f"miss{os.environ['MASTER_PORT']}"
+    ch = _FdChannel(job, rank, world, timeout_s=0.5)
+    dist.barrier()
+    me = types.SimpleNamespace(world=world, pg=None)
+    me._all_gather_obj = types.MethodType(Communicator._all_gather_obj, me)
+
+    def exchange():
+        with tempfile.TemporaryFile() as f:
+            if rank != world - 1:                           # the faulty rank keeps its handles to itself
+                for dst in range(world):
+                    if dst != rank:
+                        ch.send(dst, [os.dup(f.fileno())], tag=0)
+            for _ in range(world - 1):
+                _src, _tag, fds = ch.recv()
+                for fd in fds:
+                    os.close(fd)
+
+    with pytest.raises(PcclError) as err:
+        Communicator._agree(me, exchange)
+    assert "timed out" in str(err.value).lower() or "timeout" in str(err.value).lower()
+    ch.close()
+    t = torch.ones(1)
+    dist.all_reduce(t)                                      # the process group is still usable
+    assert int(t.item()) == world
+
+
+def test_peer_missing_at_handle_exchange_raises_everywhere(port):
+    run_ranks(_peer_missing_at_handle_exchange, 3, port)
