@@ -118,9 +118,11 @@ def tuning_rows(points: List[Dict]) -> List[List]:
         if "direct" not in prefs:
             prefs.append("direct")
         key_bytes = p["per_rank_bytes"]
-        if p["collective"] == "reduce_scatter":
+        is_rs = p["collective"] == "reduce_scatter"
+        if is_rs:
             key_bytes //= p["P"]
-        lanes = 32 if key_bytes <= (4 << 20) else 64
+        # small all-gathers: at most 32 lanes; reduce-scatters take 64 throughout (the tuner still caps by size)
+        lanes = 32 if key_bytes <= (4 << 20) and not is_rs else 64
         if rows and rows[-1][1][:3] == prefs[:3] and rows[-1][2] == lanes:
             rows[-1][0] = key_bytes
         else:

@@ -24,6 +24,7 @@ TABLE_PATH = Path(__file__).resolve().parent / "tuning_table.json"
 
 # Fallback when the table has no row: bytes each lane should at least move, lane ceiling.
 MIN_BYTES_PER_LANE = 64 << 10
+BULK_MIN_BYTES = 192 << 10      # per-lane share from which the kernels use the bulk-copy pipeline (kBulkMinBytes)
 DEFAULT_MAX_LANES = 148
 
 
@@ -99,5 +100,16 @@ def choose(collective: str, world: int, nbytes: int, *, requested: str = sch.AUT
             sch.check_algo(algo, world)   # raises: the caller asked for it explicitly
         algo = sch.DIRECT
     if lanes is None:
-        lanes = int(env_lanes) if env_lanes else min(picked_lanes or 64, default_lanes(nbytes, max_lanes))
+        # A lane of a reduce-scatter reads its share of the block from every peer, and below the bulk-copy
+        # threshold it does so in dependent rounds of a few vectors per thread: the share shrinks with the
+        # number of peers (measured at P = 4: 256 KiB blocks, 16 lanes 31 us, 4 lanes 42 us).
+        scaled = nbytes * max(1, world - 1) if collective == "reduce_scatter" else nbytes
+        lanes = int(env_lanes) if env_lanes else min(picked_lanes or 64, default_lanes(scaled, max_lanes))
+        if collective == "reduce_scatter" and not env_lanes and lanes > 0:
+            # Shares between 64 KiB and the 192 KiB from which a lane uses the bulk-copy pipeline are the slow
+            # zone of the thread-loop path (measured at P = 4, 8 MiB blocks: 64 lanes 104 us, 32 lanes 65 us):
+            # take fewer lanes so that every share reaches the pipeline.
+            share = nbytes // lanes
+            if MIN_BYTES_PER_LANE < share < BULK_MIN_BYTES:
+                lanes = max(1, nbytes // BULK_MIN_BYTES)
     return algo, max(1, min(int(lanes), max_lanes))
