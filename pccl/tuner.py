@@ -24,7 +24,7 @@ TABLE_PATH = Path(__file__).resolve().parent / "tuning_table.json"
 
 # Fallback when the table has no row: bytes each lane should at least move, lane ceiling.
 MIN_BYTES_PER_LANE = 64 << 10
-BULK_MIN_BYTES = 192 << 10      # per-lane share from which the kernels use the bulk-copy pipeline (kBulkMinBytes)
+PIPELINE_BYTES_PER_LANE = 256 << 10   # per-lane share that fills the bulk-copy pipeline (the kernels switch to it at 192 KiB)
 DEFAULT_MAX_LANES = 148
 
 
@@ -106,10 +106,11 @@ def choose(collective: str, world: int, nbytes: int, *, requested: str = sch.AUT
         scaled = nbytes * max(1, world - 1) if collective == "reduce_scatter" else nbytes
         lanes = int(env_lanes) if env_lanes else min(picked_lanes or 64, default_lanes(scaled, max_lanes))
         if collective == "reduce_scatter" and not env_lanes and lanes > 0:
-            # Shares between 64 KiB and the 192 KiB from which a lane uses the bulk-copy pipeline are the slow
-            # zone of the thread-loop path (measured at P = 4, 8 MiB blocks: 64 lanes 104 us, 32 lanes 65 us):
-            # take fewer lanes so that every share reaches the pipeline.
+            # Shares between 64 KiB and 256 KiB are the slow zone: below 192 KiB a lane runs thread loops in
+            # dependent rounds, and at 192 KiB the bulk-copy pipeline is too short to fill (measured at P = 4:
+            # 8 MiB blocks, 64 lanes 104 us, 32 lanes 65 us; 12 MiB blocks at exactly 192 KiB per lane 132 us
+            # against 106 us for 16 MiB blocks at 256 KiB).  Take fewer lanes of 256 KiB each.
             share = nbytes // lanes
-            if MIN_BYTES_PER_LANE < share < BULK_MIN_BYTES:
-                lanes = max(1, nbytes // BULK_MIN_BYTES)
+            if MIN_BYTES_PER_LANE < share < PIPELINE_BYTES_PER_LANE:
+                lanes = max(1, nbytes // PIPELINE_BYTES_PER_LANE)
     return algo, max(1, min(int(lanes), max_lanes))
