@@ -425,3 +425,29 @@ def test_tuner_takes_the_eager_variant_only_where_it_fits(monkeypatch, tmp_path)
     finally:
         monkeypatch.undo()
         tuner.reload_table()
+
+
+def test_reduce_scatter_lanes_follow_the_peer_count_and_skip_the_slow_zone(monkeypatch):
+    """Lane counts the tuner picks when the caller passes none: all-gather shares are at least
+    64 KiB per lane; a reduce-scatter lane reads from every peer, so its share shrinks with the
+    group; shares between 64 KiB and 256 KiB (thread loops in dependent rounds, or a bulk-copy
+    pipeline too short to fill) are avoided by taking fewer lanes of 256 KiB."""
+    from pccl import tuner
+
+    monkeypatch.delenv("PCCL_LANES", raising=False)
+    monkeypatch.delenv("PCCL_ALGO", raising=False)
+
+    def lanes(coll, P, nbytes):
+        return tuner.choose(coll, P, nbytes, requested="pull" if coll == "reduce_scatter" else "direct",
+                            symmetric_in=True, symmetric_out=True)[1]
+
+    assert lanes("all_gather", 8, 1 << 20) == 16                      # 64 KiB per lane
+    assert lanes("reduce_scatter", 2, 1 << 20) == 16                  # one peer: the same
+    assert lanes("reduce_scatter", 4, 1 << 20) == 48                  # three peers: a third of the share
+    assert lanes("reduce_scatter", 8, 256 << 10) == 28
+    for P in (2, 4, 8):
+        for block in (5 << 20, 8 << 20, 12 << 20):
+            n = lanes("reduce_scatter", P, block)
+            assert block // n >= 256 << 10, (P, block, n)             # out of the slow zone
+        assert lanes("reduce_scatter", P, 4 << 20) == 64              # 64 KiB shares stay
+    assert lanes("reduce_scatter", 4, 1 << 20) <= 64 and tuner.choose("reduce_scatter", 4, 1 << 20, lanes=7)[1] == 7
