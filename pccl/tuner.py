@@ -103,14 +103,17 @@ def choose(collective: str, world: int, nbytes: int, *, requested: str = sch.AUT
         # A lane of a reduce-scatter reads its share of the block from every peer, and below the bulk-copy
         # threshold it does so in dependent rounds of a few vectors per thread: the share shrinks with the
         # number of peers (measured at P = 4: 256 KiB blocks, 16 lanes 31 us, 4 lanes 42 us).
-        scaled = nbytes * max(1, world - 1) if collective == "reduce_scatter" else nbytes
+        peer_reads = collective == "reduce_scatter" and algo != sch.MULTIMEM      # the switch variant reads once
+        scaled = nbytes * max(1, world - 1) if peer_reads else nbytes
         lanes = int(env_lanes) if env_lanes else min(picked_lanes or 64, default_lanes(scaled, max_lanes))
-        if collective == "reduce_scatter" and not env_lanes and lanes > 0:
-            # Shares between 64 KiB and 256 KiB are the slow zone: below 192 KiB a lane runs thread loops in
-            # dependent rounds, and at 192 KiB the bulk-copy pipeline is too short to fill (measured at P = 4:
-            # 8 MiB blocks, 64 lanes 104 us, 32 lanes 65 us; 12 MiB blocks at exactly 192 KiB per lane 132 us
-            # against 106 us for 16 MiB blocks at 256 KiB).  Take fewer lanes of 256 KiB each.
+        if collective == "reduce_scatter" and not env_lanes and lanes > 0 and algo != sch.MULTIMEM:
+            # Shares between 64 KiB and 256 KiB are the slow zone of the peer-memory variants: below 192 KiB a
+            # lane runs thread loops in dependent rounds, and at 192 KiB the bulk-copy pipeline is too short to
+            # fill (measured at P = 4: 8 MiB blocks, 64 lanes 104 us, 32 lanes 65 us; 12 MiB blocks at exactly
+            # 192 KiB per lane 132 us against 106 us for 16 MiB blocks at 256 KiB).  Take fewer lanes of 256 KiB
+            # each, but never fewer than 32: below that the lanes themselves bound the bandwidth.
             share = nbytes // lanes
-            if MIN_BYTES_PER_LANE < share < PIPELINE_BYTES_PER_LANE:
-                lanes = max(1, nbytes // PIPELINE_BYTES_PER_LANE)
+            fewer = nbytes // PIPELINE_BYTES_PER_LANE
+            if MIN_BYTES_PER_LANE < share < PIPELINE_BYTES_PER_LANE and fewer >= 32:
+                lanes = fewer
     return algo, max(1, min(int(lanes), max_lanes))

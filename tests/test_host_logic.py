@@ -446,8 +446,10 @@ def test_reduce_scatter_lanes_follow_the_peer_count_and_skip_the_slow_zone(monke
     assert lanes("reduce_scatter", 4, 1 << 20) == 48                  # three peers: a third of the share
     assert lanes("reduce_scatter", 8, 256 << 10) == 28
     for P in (2, 4, 8):
-        for block in (5 << 20, 8 << 20, 12 << 20):
+        for block in (8 << 20, 12 << 20):
             n = lanes("reduce_scatter", P, block)
-            assert block // n >= 256 << 10, (P, block, n)             # out of the slow zone
+            assert block // n >= 256 << 10 and n >= 32, (P, block, n)  # out of the slow zone, still 32 lanes or more
         assert lanes("reduce_scatter", P, 4 << 20) == 64              # 64 KiB shares stay
+        assert lanes("reduce_scatter", P, 5 << 20) == 64              # too small for 32 lanes of 256 KiB: unchanged
+    assert tuner.choose("reduce_scatter", 8, 8 << 20, requested="multimem", symmetric_in=True, has_multimem=True)[1] == 64
     assert lanes("reduce_scatter", 4, 1 << 20) <= 64 and tuner.choose("reduce_scatter", 4, 1 << 20, lanes=7)[1] == 7
