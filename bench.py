@@ -19,11 +19,15 @@ explicit flush is needed between steps.  A second pass measures the same K steps
 end through ``Zero3Engine.train_step`` fed from pinned host memory, reading the loss back
 to the host every step.
 
-The default run measures two arms back to back in one process, same steps and warm-up:
-the library arm (collectives, GEMMs and element-wise kernels of this repository) and the
-baseline arm the reference's NCCL build amounts to (the same engine with its collectives on
-``torch.distributed``/NCCL and every dense product on cuBLAS through ``torch``).
-``vs_baseline`` is the ratio of the two; the reference publishes no number of its own.
+The default run measures three arms back to back in one process, same steps and warm-up:
+the library arm (collectives and element-wise kernels of this repository; plain dense
+products on cuBLAS, ``--gemm auto``), the same arm with every dense product on this
+repository's tcgen05 GEMM (``native_gemm_arm`` in the JSON line; ``--gemm pccl`` makes it the
+main arm) and the baseline arm the reference's NCCL build amounts to (the same engine with its
+collectives on ``torch.distributed``/NCCL and every dense product on cuBLAS through
+``torch``).  ``vs_baseline`` is library arm / baseline arm; the reference publishes no number
+of its own, and what it patches is DeepSpeed's backend (``pccl/patch_deepspeed.py:95-126`` of
+the reference), which is what ``pccl.patch_deepspeed`` re-routes here.
 
 The reference itself has no model and no training loop, so ``--impl reference`` cannot produce
 tokens/s; it prints the ``unavailable`` line and, as evidence for the other half of the metric,

@@ -9,7 +9,8 @@ reference's NCCL path, ``dist.all_gather_into_tensor`` on the world group; ``mpi
 available here (no MPI implementation) and is refused.
 
 Two sweeps:
-  ``--size-mode output``  the reference's: TOTAL OUTPUT 1..1024 MiB, per-rank input = output / world
+  ``--size-mode output``  the reference's (``benchmark_raw_collectives/all_gather.py:54-55,86-92``):
+                          TOTAL OUTPUT 1..1024 MiB, per-rank input = output / world
   ``--size-mode input``   PER-RANK INPUT 1 MiB..1 GiB (default)
 Times are device-timed, 5 warm-up + 20 timed calls, maximum over ranks; every row reports bus
 bandwidth and its fraction of the 900 GB/s per-direction NVLink roofline.
