@@ -453,3 +453,24 @@ def test_reduce_scatter_lanes_follow_the_peer_count_and_skip_the_slow_zone(monke
         assert lanes("reduce_scatter", P, 5 << 20) == 64              # too small for 32 lanes of 256 KiB: unchanged
     assert tuner.choose("reduce_scatter", 8, 8 << 20, requested="multimem", symmetric_in=True, has_multimem=True)[1] == 64
     assert lanes("reduce_scatter", 4, 1 << 20) <= 64 and tuner.choose("reduce_scatter", 4, 1 << 20, lanes=7)[1] == 7
+
+
+def test_sweep_markdown_handles_lane_suffixed_variants():
+    """``sweep.py --lanes a,b,c`` names its columns ``variant@lanes``; the markdown table lists them all."""
+    import importlib.util
+    from pathlib import Path
+
+    path = Path(__file__).resolve().parent.parent / "benchmark_raw_collectives" / "sweep.py"
+    spec = importlib.util.spec_from_file_location("pccl_sweep_for_test", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    best = {"variant": "pull@64", "ms": 0.04, "busbw_gbs": 150.0, "vs_nccl": 1.3, "correct": None,
+            "frac_of_900": 0.16, "frac_of_measured_770": 0.19}
+    doc = {"P": 4, "nvls": True, "transport": "vmm", "timing": "t",
+           "rows": [{"sweep": "rs", "collective": "reduce_scatter", "P": 4, "dtype": "bfloat16", "per_rank_bytes": 8 << 20,
+                     "nccl_ms": 0.05, "nccl_busbw_gbs": 100.0,
+                     "variants": {"pull@4": {"ms": 0.07, "busbw_gbs": 80.0, "vs_nccl": 0.7, "correct": None},
+                                  "pull@64": {"ms": 0.04, "busbw_gbs": 150.0, "vs_nccl": 1.3, "correct": None}},
+                     "best": best, "best_without_multimem": best}]}
+    text = mod.markdown(doc)
+    assert "pull@4 µs" in text and "pull@64 µs" in text and "| 8 | 50.0 |" in text
